@@ -1,0 +1,192 @@
+/*
+ * trifast_b200 — C ABI of the B200 (sm_100a) triangle self-attention kernels.
+ *
+ * This is the boundary a host binding attaches to: plain pointers, sizes and
+ * element strides, no C++ or torch types.  It replaces the launch layer of the
+ * reference (latkins/trifast), where Python code in src/trifast/torch.py
+ * allocates the outputs and launches four Triton kernels; each entry point
+ * below names the reference code it stands in for.
+ *
+ * Tensors (layout of src/trifast/torch.py:220-226 of the reference):
+ *   q, k, v, o, dO, dq, dk, dv : (batch, heads, n_rows, n, d), innermost d contiguous
+ *   bias, db                   : (batch, heads, n, n) = (b, h, j, k), innermost contiguous
+ *   mask                       : (batch, n_rows, n) = (b, i, k), one byte per key,
+ *                                non-zero = key k is masked OUT for pair row i
+ *   lse, delta                 : (batch, heads, n_rows, n) fp32, contiguous
+ * n_rows is the number of pair rows i held by this call: n for the whole
+ * problem, fewer for a row shard (rows are independent except for db, which is
+ * then a partial sum over the local rows).
+ *
+ * Ownership: the caller owns every buffer, including the workspace.  No entry
+ * point allocates, frees or synchronises device memory unless its comment says
+ * otherwise.  Outputs are fully overwritten.  All work is enqueued on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *
+ * Errors: every function returns TRIFAST_OK (0) or a negative trifast_status;
+ * nothing throws across this boundary.  trifast_status_str() names a code.
+ */
+#ifndef TRIFAST_B200_H_
+#define TRIFAST_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum trifast_status {
+  TRIFAST_OK = 0,
+  TRIFAST_ERR_NULL = -1,          /* a required pointer is NULL */
+  TRIFAST_ERR_SHAPE = -2,         /* non-positive extent, n_rows > n, ... */
+  TRIFAST_ERR_HEAD_DIM = -3,      /* d is not one of 16, 32, 64, 128 */
+  TRIFAST_ERR_DTYPE = -4,         /* unknown trifast_dtype */
+  TRIFAST_ERR_STRIDE = -5,        /* negative stride / stride breaks 16-byte rule */
+  TRIFAST_ERR_ALIGN = -6,         /* a base pointer is not 16-byte aligned */
+  TRIFAST_ERR_WORKSPACE = -7,     /* workspace missing or too small */
+  TRIFAST_ERR_ARCH = -8,          /* device is not compute capability 10.x */
+  TRIFAST_ERR_LAUNCH = -9,        /* CUDA reported an error at launch */
+  TRIFAST_ERR_KERNEL_CHOICE = -10,/* forced kernel cannot run this problem */
+  TRIFAST_ERR_DEVICE_TIMEOUT = -11,/* a bounded wait inside a kernel gave up */
+  TRIFAST_ERR_TOO_LARGE = -12     /* size beyond a stated maximum */
+} trifast_status;
+
+typedef enum trifast_dtype {
+  TRIFAST_F32 = 0,
+  TRIFAST_BF16 = 1,
+  TRIFAST_F16 = 2
+} trifast_dtype;
+
+/* Which kernel family runs.  AUTO applies the fixed heuristic keyed on
+ * (n, h, d, dtype) that replaces the reference's benchmark-and-cache autotuner
+ * (src/trifast/autotune.py:28-156, config lists autotune_helpers.py:58-211). */
+typedef enum trifast_kernel {
+  TRIFAST_KERNEL_AUTO = 0,
+  TRIFAST_KERNEL_SIMT = 1,   /* fp32-accumulate CUDA-core kernels: any dtype, any n */
+  TRIFAST_KERNEL_TCGEN05 = 2 /* tcgen05 / TMEM / TMA kernels: bf16 and fp16 */
+} trifast_kernel;
+
+/* Problem extents, shared by every call. */
+typedef struct trifast_shape {
+  int32_t batch;
+  int32_t heads;
+  int32_t n;       /* keys per row = queries per row */
+  int32_t n_rows;  /* pair rows i in this call (<= n) */
+  int32_t d;       /* head dim: 16, 32, 64 or 128 */
+  int32_t dtype;   /* trifast_dtype of q, k, v, bias, o and the gradients */
+  int32_t kernel;  /* trifast_kernel; 0 = heuristic */
+  int32_t reserved;
+} trifast_shape;
+
+/* (b, h, i, j, d) tensor: strides in elements for b, h, i, j; d has stride 1. */
+typedef struct trifast_t5 {
+  void* data;
+  int64_t stride[4];
+} trifast_t5;
+
+/* (b, h, j, k) tensor: strides in elements for b, h, j; k has stride 1. */
+typedef struct trifast_t4 {
+  void* data;
+  int64_t stride[3];
+} trifast_t4;
+
+/* (b, i, k) byte mask: strides in bytes for b, i; k has stride 1. */
+typedef struct trifast_mask {
+  const uint8_t* data;
+  int64_t stride[2];
+} trifast_mask;
+
+/* Tile plan chosen by the heuristic (host only; no device needed). */
+typedef struct trifast_plan {
+  int32_t kernel;        /* trifast_kernel actually used */
+  int32_t block_j;       /* query tile */
+  int32_t block_k;       /* key tile */
+  int32_t rows_per_cta;  /* pair rows sharing one bias tile in the forward */
+  int32_t stages;        /* K/V/bias pipeline depth */
+  int32_t db_row_splits; /* row groups whose db partials are summed in fixed order */
+  int32_t reserved[2];
+} trifast_plan;
+
+/* Library version as major*10000 + minor*100 + patch. */
+int trifast_version(void);
+
+/* Text for a status code (static storage). */
+const char* trifast_status_str(int status);
+
+/* Fixed tile heuristic.  Stands in for Autotuner.run of the reference
+ * (src/trifast/autotune.py:110-156): same key (n, h, d, dtype), but a table
+ * instead of benchmarking and an on-disk cache.  Pure host code. */
+int trifast_pick_plan(const trifast_shape* shape, trifast_plan* plan);
+
+/* Bytes of caller-provided workspace the backward needs (delta + db partials).
+ * The forward needs none.  Returns 0 on an invalid shape. */
+size_t trifast_backward_workspace_bytes(const trifast_shape* shape);
+
+/* Forward: o = softmax_k(q.k^T * d^-0.5 + bias + mask) v and lse (natural log).
+ * Stands in for _triangle_attention + the _fwd kernel of the reference
+ * (src/trifast/torch.py:17-65, src/trifast/triton.py:14-132).
+ * Rows whose keys are all masked get uniform weights 1/n over all n keys, as
+ * the reference's PyTorch path does (src/trifast/equiv.py:42-69); their lse is
+ * stored as finfo(dtype).min. */
+int trifast_forward(const trifast_shape* shape,
+                    const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+                    const trifast_t4* bias, const trifast_mask* mask,
+                    const trifast_t5* o, float* lse, void* stream);
+
+/* Whole backward on one device: dq, dk, dv and db (db in the input dtype).
+ * Stands in for triangle_attention_bwd and its three kernels
+ * (src/trifast/torch.py:68-182; triton.py:268-383 _bwd_q, :137-263 _bwd_kv,
+ * :388-501 _bwd_b).  `workspace` holds at least
+ * trifast_backward_workspace_bytes() bytes.  db is reduced over rows in a fixed
+ * order (deterministic, no atomics). */
+int trifast_backward(const trifast_shape* shape,
+                     const trifast_t5* d_o,
+                     const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+                     const trifast_t4* bias, const trifast_mask* mask,
+                     const trifast_t5* o, const float* lse,
+                     const trifast_t5* dq, const trifast_t5* dk, const trifast_t5* dv,
+                     const trifast_t4* db,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* The backward in three steps, for row-sharded runs that overlap the
+ * all-reduce of db with the rest of the backward.  The reference has no
+ * multi-device path; these split triangle_attention_bwd
+ * (src/trifast/torch.py:68-182) at the points where the exchange happens.
+ *
+ * 1. trifast_backward_db: delta = sum_d o*dO (kept fp32 inside the workspace)
+ *    and the partial bias gradient over the local rows, written as fp32
+ *    (batch, heads, n, n) contiguous into db_f32.
+ * 2. (caller) all-reduce db_f32 across row shards on another stream.
+ * 3. trifast_backward_dqkv: dq, dk, dv; reads the delta step 1 left in the
+ *    same workspace.
+ * 4. trifast_db_finalize: round the summed fp32 db to the input dtype. */
+int trifast_backward_db(const trifast_shape* shape,
+                        const trifast_t5* d_o,
+                        const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+                        const trifast_t4* bias, const trifast_mask* mask,
+                        const trifast_t5* o, const float* lse,
+                        float* db_f32,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+int trifast_backward_dqkv(const trifast_shape* shape,
+                          const trifast_t5* d_o,
+                          const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+                          const trifast_t4* bias, const trifast_mask* mask,
+                          const float* lse,
+                          const trifast_t5* dq, const trifast_t5* dk, const trifast_t5* dv,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
+                        const trifast_t4* db, void* stream);
+
+/* Reads and clears the per-device status word that kernels set when one of
+ * their bounded waits gives up.  Synchronises `stream` first.  Returns
+ * TRIFAST_OK or TRIFAST_ERR_DEVICE_TIMEOUT.  (No reference counterpart: Triton
+ * kernels have no such waits.) */
+int trifast_check_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TRIFAST_B200_H_ */

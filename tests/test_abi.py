@@ -1,0 +1,132 @@
+"""CPU tier: the C-ABI library loads, exports every symbol the header declares,
+validates arguments before touching a device, and the tile heuristic is a pure
+host function."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from trifast_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "trifast_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(trifast_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.load()
+    names = header_symbols()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.trifast_version() >= 100
+    assert _lib.status_str(0) == "ok"
+    for rc in range(-12, 0):
+        assert _lib.status_str(rc) != "unknown status"
+    assert _lib.status_str(-99) == "unknown status"
+
+
+@pytest.mark.parametrize("n,h,d,dtype,kernel", [
+    (1024, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),
+    (2048, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),
+    (1024, 8, 64, torch.float16, _lib.KERNEL_TCGEN05),
+    (256, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),
+    (32, 4, 32, torch.float32, _lib.KERNEL_SIMT),     # fp32 always on CUDA cores
+    (1024, 4, 32, torch.float32, _lib.KERNEL_SIMT),
+    (191, 4, 32, torch.bfloat16, _lib.KERNEL_SIMT),   # bias row pitch not 16-byte
+    (64, 1, 64, torch.bfloat16, _lib.KERNEL_SIMT),    # below one tile
+    (256, 4, 128, torch.bfloat16, _lib.KERNEL_SIMT),
+    (256, 4, 16, torch.float16, _lib.KERNEL_SIMT),
+])
+def test_heuristic_table(n, h, d, dtype, kernel):
+    plan = _lib.pick_plan(1, h, n, n, d, dtype)
+    assert plan["kernel"] == kernel
+    assert plan["db_row_splits"] >= 1
+    if kernel == _lib.KERNEL_TCGEN05:
+        assert (plan["block_j"], plan["block_k"]) == (128, 128)
+
+
+def test_heuristic_rejects_impossible_forced_kernel():
+    shp = _lib.make_shape(1, 4, 191, 191, 32, torch.bfloat16, _lib.KERNEL_TCGEN05)
+    plan = _lib.Plan()
+    assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == -10
+
+
+def test_db_splits_cover_small_problems():
+    assert _lib.pick_plan(1, 1, 64, 64, 32, torch.float32)["db_row_splits"] > 1
+    assert _lib.pick_plan(1, 4, 1024, 1024, 32, torch.float32)["db_row_splits"] == 1
+
+
+@pytest.mark.parametrize("kw,rc", [
+    (dict(n=0), -2), (dict(n_rows=65), -2), (dict(d=48), -3), (dict(dtype=7), -4),
+    (dict(batch=0), -2), (dict(kernel=9), -10),
+])
+def test_shape_validation(kw, rc):
+    f = dict(batch=1, heads=2, n=64, n_rows=64, d=32, dtype=1, kernel=0, reserved=0)
+    f.update(kw)
+    shp = _lib.Shape(**f)
+    plan = _lib.Plan()
+    assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == rc
+    assert _lib.load().trifast_backward_workspace_bytes(C.byref(shp)) == 0
+
+
+def _fake5(ptr=0x1000, stride=(64 * 64 * 32 * 2, 64 * 64 * 32, 64 * 32, 32)):
+    return _lib.T5(ptr, (C.c_int64 * 4)(*stride))
+
+
+def test_forward_argument_validation_needs_no_device():
+    lib = _lib.load()
+    shp = _lib.make_shape(1, 2, 64, 64, 32, torch.bfloat16, 0)
+    t, bias = _fake5(), _lib.T4(0x1000, (C.c_int64 * 3)(2 * 64 * 64, 64 * 64, 64))
+    mask = _lib.Mask(0x1000, (C.c_int64 * 2)(64 * 64, 64))
+    lse = C.c_void_p(0x1000)
+
+    def call(q=t, k=t, v=t, b=bias, m=mask, o=t, l=lse):
+        return lib.trifast_forward(C.byref(shp), C.byref(q), C.byref(k), C.byref(v), C.byref(b),
+                                   C.byref(m), C.byref(o), l, None)
+
+    assert call(q=_fake5(ptr=0)) == -1                       # NULL data
+    assert call(k=_fake5(ptr=0x1008)) == -6                  # misaligned
+    assert call(v=_fake5(stride=(1, 1, 1, 31))) == -5        # stride not 16-byte multiple
+    assert call(v=_fake5(stride=(0, 0, 0, 16))) == -5        # rows overlap
+    assert call(b=_lib.T4(0x1000, (C.c_int64 * 3)(0, 0, 8))) == -5
+    assert call(m=_lib.Mask(0x1000, (C.c_int64 * 2)(0, 8))) == -5
+    assert call(l=None) == -1
+
+
+def test_workspace_size_formula():
+    lib = _lib.load()
+    shp = _lib.make_shape(1, 4, 1024, 1024, 32, torch.bfloat16)
+    ws = lib.trifast_backward_workspace_bytes(C.byref(shp))
+    stat = 4 * 1024 * 1024 * 4
+    assert ws >= 2 * stat and ws < 2 * stat + (1 << 20)       # delta + fp32 db (+ small)
+    shard = _lib.make_shape(1, 4, 1024, 128, 32, torch.bfloat16)
+    assert lib.trifast_backward_workspace_bytes(C.byref(shard)) < ws
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libtrifast_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+
+
+def test_cpu_tensors_are_rejected():
+    from trifast_b200 import triangle_attention
+    from trifast_b200.utils import gen_tensors
+    q, k, v, b, m = gen_tensors(16, 16, 1, False, "cpu", torch.float32)
+    with pytest.raises(Exception):
+        triangle_attention(q, k, v, b, m)

@@ -1,0 +1,244 @@
+"""GPU tier: the CUDA path (through the public op, i.e. through the C ABI) against
+the CPU oracle and the reference-generated golden vectors.
+
+Tolerances
+* fp32: max|x - ref| / max|ref| <= 1e-4 against the fp64 oracle, for o, dq, dk, dv, db.
+* bf16 / fp16: the reference's own rule (tests/utils.py:31-36 there): kernel error
+  <= 3 * (error of PyTorch run in the same dtype + eps), eps = 1e-3, plus its
+  direction rules (cosine > 0.99, >= 0.99 * PyTorch's, projection within 0.01).
+* masked keys: exactly zero weight (bitwise-identical outputs when masked k/v change).
+"""
+
+import pytest
+import torch
+
+from oracle import triangle_oracle as orc
+from tests.helpers import (DTYPE_EPS, FP32_REL_TOL, assert_direction, assert_within_pt_error,
+                           golden_cases, load_golden, rel_err)
+from trifast_b200 import triangle_attention
+from trifast_b200.configs import WORKLOADS, make_inputs
+from trifast_b200.utils import gen_tensors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+NAMES = ("o", "dq", "dk", "dv", "db")
+
+
+def run_kernel(q, k, v, b, m, do):
+    q, k, v, b = (t.detach().to(DEV).requires_grad_(True) for t in (q, k, v, b))
+    o = triangle_attention(q, k, v, b, m.to(DEV))
+    o.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    return tuple(t.detach().float().cpu() for t in (o, q.grad, k.grad, v.grad, b.grad))
+
+
+def run_oracle64(q, k, v, b, m, do):
+    o, _ = orc.forward(q, k, v, b, m, torch.float64)
+    return (o,) + orc.backward(do, q, k, v, b, m, torch.float64)
+
+
+def run_pt(q, k, v, b, m, do):
+    """PyTorch in the inputs' dtype on the CPU (the error bar of the relative rule)."""
+    q, k, v, b = (t.detach().clone().requires_grad_(True) for t in (q, k, v, b))
+    o = orc.attention_reference_port(q, k, v, b, m)
+    o.backward(do)
+    return tuple(t.detach().float() for t in (o, q.grad, k.grad, v.grad, b.grad))
+
+
+def check(dtype, got, ref, pt, tag):
+    for name, g, r, p in zip(NAMES, got, ref, pt if pt is not None else ref):
+        if dtype == torch.float32:
+            e = rel_err(g, r)
+            assert e <= FP32_REL_TOL, f"{tag} {name}: rel err {e:.3e} > {FP32_REL_TOL}"
+        else:
+            assert_within_pt_error(g, p, r, DTYPE_EPS[dtype], f"{tag} {name}")
+            assert_direction(g, p, r, f"{tag} {name}")
+
+
+@pytest.mark.parametrize("case", golden_cases())
+def test_golden_vectors(case):
+    t, dtype = load_golden(case)
+    args = tuple(t[x].to(dtype) for x in ("q", "k", "v", "bias")) + (t["mask"], t["do"].to(dtype))
+    got = run_kernel(*args)
+    stored = tuple(t[x] for x in NAMES)
+    if dtype == torch.float32:
+        check(dtype, got, stored, None, case)      # the reference's own fp32 results
+    else:
+        ref = run_oracle64(*args)
+        check(dtype, got, ref, stored, case)       # stored = the reference run in bf16
+
+
+def seeded(n, h, d, dtype, use_mask, bs, std, seed=1337):
+    torch.manual_seed(seed)
+    q, k, v, b, m = gen_tensors(n, d, h, use_mask, "cpu", torch.float32, batch=bs, std=std)
+    do = torch.randn(q.shape)
+    return tuple(t.detach().to(dtype) for t in (q, k, v, b)) + (m, do.to(dtype))
+
+
+SHAPES = [(16, 1, 16), (32, 1, 32), (64, 1, 64), (16, 4, 128), (191, 4, 32)] + \
+         [(n, 4, 32) for n in (17, 31, 33, 63, 65, 96, 100, 127, 128, 129, 136, 160, 199)] + \
+         [(128, 2, 64), (144, 2, 64), (256, 2, 32), (264, 1, 32)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("use_mask", [True, False])
+@pytest.mark.parametrize("n,h,d", SHAPES)
+def test_values_and_directions(n, h, d, dtype, use_mask):
+    """The reference's test_values / test_vectors matrix (tests/unit/test_trifast.py:26-149),
+    thinned in n, with random dO instead of ones."""
+    bs, std = (2, 2.0) if n % 2 else (1, 1.0)
+    args = seeded(n, h, d, dtype, use_mask, bs, std)
+    got = run_kernel(*args)
+    ref = run_oracle64(*args)
+    pt = None if dtype == torch.float32 else run_pt(*args)
+    check(dtype, got, ref, pt, f"n={n} h={h} d={d} {dtype} mask={use_mask}")
+
+
+@pytest.mark.parametrize("name", ["c1_cpu_plumbing", "c2_n256", "c3_n512_pad"])
+def test_named_workloads(name):
+    w = WORKLOADS[name]
+    args = make_inputs(w, seed=1337)
+    got = run_kernel(*args)
+    q, k, v, b, m, do = args
+    o, lse, grads = orc.forward_backward_chunked(q, k, v, b, m, do=do, rows_per_chunk=16,
+                                                 acc_dtype=torch.float64)
+    ref = (o,) + grads
+    pt = None
+    if w.dtype != torch.float32:
+        # same-dtype PyTorch error bar, row-chunked (rows are independent; db adds up)
+        parts = [run_pt(q[:, :, r:r + 32], k[:, :, r:r + 32], v[:, :, r:r + 32], b,
+                        m[:, r:r + 32], do[:, :, r:r + 32]) for r in range(0, w.n, 32)]
+        pt = tuple(torch.cat([p[x] for p in parts], dim=2) for x in range(4)) + \
+            (sum(p[4] for p in parts),)
+    check(w.dtype, got, ref, pt, name)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [48, 256])
+def test_masked_keys_have_exactly_zero_weight(dtype, n):
+    q, k, v, b, m, do = seeded(n, 2, 32, dtype, True, 1, 1.0, seed=5)
+    m[0, 3] = True                                     # one fully masked row as well
+    partial = ~m.all(dim=-1)
+    sel = (m & partial[..., None])[:, None, :, :, None].expand_as(v)
+    v2, k2 = v.clone(), k.clone()
+    v2[sel] = 77.0
+    k2[sel] = -55.0
+    a = run_kernel(q, k, v, b, m, do)
+    c = run_kernel(q, k2, v2, b, m, do)
+    assert torch.equal(a[0], c[0]), "o changed when masked k/v changed"
+    # masked keys of partially masked rows receive exactly zero dk, dv
+    assert float(a[2][sel].abs().max()) == 0.0 and float(a[3][sel].abs().max()) == 0.0
+    # the fully masked row is the mean of v
+    mean_v = v[0, :, 3].float().mean(dim=1)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert float((a[0][0, :, 3] - mean_v[:, None, :]).abs().max()) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_shards_match_whole_problem(dtype):
+    """Rows are independent: running rows [r0, r1) alone gives the same o, dq, dk, dv,
+    bit for bit, and the shard db partials add up to the whole db."""
+    n = 136
+    q, k, v, b, m, do = seeded(n, 2, 32, dtype, True, 1, 1.0, seed=9)
+    whole = run_kernel(q, k, v, b, m, do)
+    db = 0
+    for r in (slice(0, 50), slice(50, n)):
+        part = run_kernel(q[:, :, r], k[:, :, r], v[:, :, r], b, m[:, r], do[:, :, r])
+        for x in range(4):
+            assert torch.equal(part[x], whole[x][:, :, r]), NAMES[x]
+        db = db + part[4].double()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert rel_err(db, whole[4].double()) < tol
+
+
+def test_run_to_run_determinism():
+    args = seeded(160, 2, 32, torch.bfloat16, True, 1, 1.0)
+    a, c = run_kernel(*args), run_kernel(*args)
+    for x, y, name in zip(a, c, NAMES):
+        assert torch.equal(x, y), name
+
+
+def test_non_contiguous_inputs():
+    """(b, n, n, h, d) projections permuted to (b, h, n, n, d) are consumed through strides."""
+    torch.manual_seed(3)
+    n, h, d = 40, 2, 32
+    base = [torch.randn(1, n, n, h, d) for _ in range(3)]
+    q, k, v = (t.permute(0, 3, 1, 2, 4) for t in base)
+    b = torch.randn(1, n, n, h).permute(0, 3, 1, 2)
+    m = torch.rand(1, n, n) < 0.3
+    do = torch.randn(1, h, n, n, d)
+    got = run_kernel(q, k, v, b, m, do)
+    ref = run_oracle64(q, k, v, b, m, do)
+    check(torch.float32, got, ref, None, "permuted")
+
+
+def test_full_size_properties():
+    """Metric shape (n = 1024, h = 4, d = 32, bf16): properties that need no CPU oracle.
+    * with v = 1 everywhere every output is exactly 1 (weights sum to one);
+    * the forward is linear in v;
+    * a second run reproduces the first bit for bit;
+    * a 32-row sample of the output matches the oracle."""
+    w = WORKLOADS["metric_n1024"]
+    q, k, v, b, m, do = make_inputs(w, seed=1, device=DEV)
+    o1 = triangle_attention(q, k, v, b, m)
+    ones = triangle_attention(q, k, torch.ones_like(v), b, m)
+    assert float((ones.float() - 1).abs().max()) <= 2 ** -7
+    v2 = torch.randn_like(v) * 0.2
+    lin = triangle_attention(q, k, (v.float() + v2.float()).to(v.dtype), b, m).float()
+    sep = o1.float() + triangle_attention(q, k, v2, b, m).float()
+    assert float((lin - sep).abs().max()) < 3e-2
+    assert torch.equal(o1, triangle_attention(q, k, v, b, m))
+    rows = slice(500, 532)
+    ref, _ = orc.forward(q[:, :, rows].cpu(), k[:, :, rows].cpu(), v[:, :, rows].cpu(), b.cpu(),
+                         m[:, rows].cpu(), torch.float32)
+    assert rel_err(o1[:, :, rows].float().cpu(), ref) < 2e-2
+
+
+def test_opcheck():
+    """torch.library.opcheck on the forward op (tests/unit/test_trifast_opcheck.py:7-13)."""
+    from torch.library import opcheck
+    from trifast_b200.torch import _triangle_attention
+    for n, d, h in [(16, 16, 1), (128, 32, 4), (136, 64, 1)]:
+        q, k, v, b, m = gen_tensors(n, d, h, True, DEV, dtype=torch.bfloat16)
+        opcheck(_triangle_attention, (q, k, v, b, m), raise_exception=True)
+
+
+def test_torch_compile_fullgraph():
+    q, k, v, b, m = gen_tensors(64, 32, 2, True, DEV, dtype=torch.bfloat16)
+    fn = torch.compile(triangle_attention, fullgraph=True)
+    o = fn(q, k, v, b, m)
+    assert torch.equal(o, triangle_attention(q, k, v, b, m))
+    o.sum().backward()
+    assert q.grad is not None and b.grad is not None
+
+
+def test_weight_updates():
+    """Five Adam steps through a toy projection module change every parameter
+    (tests/unit/test_trifast.py:152-211 of the reference, in the canonical layout)."""
+    torch.manual_seed(0)
+    n, h, d = 32, 2, 32
+
+    class Toy(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v = (torch.nn.Linear(d, h * d) for _ in range(3))
+            self.b = torch.nn.Linear(d, h)
+
+        def forward(self, x, mask):
+            split = lambda t: t.unflatten(-1, (h, d)).permute(0, 3, 1, 2, 4)
+            return triangle_attention(split(self.q(x)), split(self.k(x)), split(self.v(x)),
+                                      self.b(x).permute(0, 3, 1, 2), mask)
+
+    model = Toy().to(DEV, torch.bfloat16)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    x = torch.randn(1, n, n, d, device=DEV, dtype=torch.bfloat16)
+    mask = torch.zeros(1, n, n, dtype=torch.bool, device=DEV)
+    before = {k: p.clone() for k, p in model.named_parameters()}
+    for _ in range(5):
+        out = model(x, mask)
+        loss = torch.nn.functional.mse_loss(out, torch.randn_like(out) * 4)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    for k, p in model.named_parameters():
+        assert not torch.equal(before[k], p), f"parameter {k} did not update"

@@ -1,0 +1,127 @@
+"""ctypes binding of ``libtrifast_b200.so`` (declarations: include/trifast_b200.h).
+
+The library is the only compute path: if it is missing or fails to load, calls
+raise instead of falling back to anything else.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtrifast_b200.so")
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+_KERNEL_ENV = {"": 0, "auto": 0, "simt": 1, "tcgen05": 2}
+
+
+class Shape(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("batch", "heads", "n", "n_rows", "d", "dtype", "kernel", "reserved")]
+
+
+class T5(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("stride", C.c_int64 * 4)]
+
+
+class T4(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("stride", C.c_int64 * 3)]
+
+
+class Mask(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("stride", C.c_int64 * 2)]
+
+
+class Plan(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("block_j", C.c_int32), ("block_k", C.c_int32),
+                ("rows_per_cta", C.c_int32), ("stages", C.c_int32), ("db_row_splits", C.c_int32),
+                ("reserved", C.c_int32 * 2)]
+
+
+# name -> (restype, argtypes); one entry per declaration in include/trifast_b200.h
+_P = C.POINTER
+SIGNATURES = {
+    "trifast_version": (C.c_int, []),
+    "trifast_status_str": (C.c_char_p, [C.c_int]),
+    "trifast_pick_plan": (C.c_int, [_P(Shape), _P(Plan)]),
+    "trifast_backward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
+    "trifast_forward": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T4), _P(Mask), _P(T5),
+                                  C.c_void_p, C.c_void_p]),
+    "trifast_backward": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4), _P(Mask),
+                                   _P(T5), C.c_void_p, _P(T5), _P(T5), _P(T5), _P(T4),
+                                   C.c_void_p, C.c_size_t, C.c_void_p]),
+    "trifast_backward_db": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4), _P(Mask),
+                                      _P(T5), C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_size_t, C.c_void_p]),
+    "trifast_backward_dqkv": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4),
+                                        _P(Mask), C.c_void_p, _P(T5), _P(T5), _P(T5),
+                                        C.c_void_p, C.c_size_t, C.c_void_p]),
+    "trifast_db_finalize": (C.c_int, [_P(Shape), C.c_void_p, _P(T4), C.c_void_p]),
+    "trifast_check_device_status": (C.c_int, [C.c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library once; raise with build instructions if it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m trifast_b200.build` "
+                "(needs nvcc; there is no fallback path)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def status_str(rc: int) -> str:
+    return load().trifast_status_str(rc).decode()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what}: {status_str(rc)} (status {rc})")
+
+
+def kernel_choice() -> int:
+    """Debug override of the tile heuristic: TRIFAST_B200_KERNEL=simt|tcgen05|auto."""
+    return _KERNEL_ENV[os.environ.get("TRIFAST_B200_KERNEL", "").lower()]
+
+
+def make_shape(batch, heads, n, n_rows, d, dtype, kernel=None) -> Shape:
+    if dtype not in DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {dtype}; expected float32, bfloat16 or float16")
+    return Shape(batch, heads, n, n_rows, d, DTYPE_CODE[dtype],
+                 kernel_choice() if kernel is None else kernel, 0)
+
+
+def t5(t: torch.Tensor) -> T5:
+    assert t.dim() == 5 and t.stride(4) == 1
+    return T5(t.data_ptr(), (C.c_int64 * 4)(*t.stride()[:4]))
+
+
+def t4(t: torch.Tensor) -> T4:
+    assert t.dim() == 4 and t.stride(3) == 1
+    return T4(t.data_ptr(), (C.c_int64 * 3)(*t.stride()[:3]))
+
+
+def mask_view(m: torch.Tensor) -> Mask:
+    assert m.dim() == 3 and m.stride(2) == 1 and m.element_size() == 1
+    return Mask(m.data_ptr(), (C.c_int64 * 2)(*m.stride()[:2]))
+
+
+def pick_plan(batch, heads, n, n_rows, d, dtype, kernel=KERNEL_AUTO) -> dict:
+    """Host-only: the tile plan the heuristic chooses for a problem."""
+    plan = Plan()
+    shp = make_shape(batch, heads, n, n_rows, d, dtype, kernel)
+    check(load().trifast_pick_plan(C.byref(shp), C.byref(plan)), "trifast_pick_plan")
+    return {f: getattr(plan, f) for f, _ in Plan._fields_ if f != "reserved"}

@@ -1,0 +1,374 @@
+// C ABI of the library: argument validation, the fixed tile heuristic, workspace
+// carving and dispatch to the kernel launchers.  Entry points are declared and
+// documented in include/trifast_b200.h.
+
+#include <float.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "kernels.h"
+
+namespace trifast {
+namespace {
+
+__device__ unsigned int g_device_status;  // OR of DeviceStatusBits
+
+constexpr int kMaxDevices = 64;
+unsigned int* g_status_ptr[kMaxDevices];
+int g_arch_major[kMaxDevices];
+std::once_flag g_once[kMaxDevices];
+
+// Per-device set-up, once: address of the status word and the compute capability.
+int device_setup(int* dev_out, unsigned int** status) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TRIFAST_ERR_LAUNCH;
+  std::call_once(g_once[dev], [dev] {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess) g_status_ptr[dev] = (unsigned int*)p;
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    g_arch_major[dev] = major;
+  });
+  if (!g_status_ptr[dev]) return TRIFAST_ERR_LAUNCH;
+  if (g_arch_major[dev] != 10) return TRIFAST_ERR_ARCH;
+  *dev_out = dev;
+  *status = g_status_ptr[dev];
+  return TRIFAST_OK;
+}
+
+int elem_bytes(int dtype) { return dtype == TRIFAST_F32 ? 4 : 2; }
+
+float dtype_sentinel(int dtype) {
+  switch (dtype) {
+    case TRIFAST_F32: return -FLT_MAX;
+    case TRIFAST_BF16: return -3.3895313892515355e38f;  // finfo(bfloat16).min
+    default: return -65504.f;                           // finfo(float16).min
+  }
+}
+
+int check_shape(const trifast_shape* s) {
+  if (!s) return TRIFAST_ERR_NULL;
+  if (s->batch <= 0 || s->heads <= 0 || s->n <= 0 || s->n_rows <= 0 || s->n_rows > s->n)
+    return TRIFAST_ERR_SHAPE;
+  if ((int64_t)s->batch * s->heads > 65535 || s->n_rows > 65535) return TRIFAST_ERR_SHAPE;
+  if (s->d != 16 && s->d != 32 && s->d != 64 && s->d != 128) return TRIFAST_ERR_HEAD_DIM;
+  if (s->dtype < TRIFAST_F32 || s->dtype > TRIFAST_F16) return TRIFAST_ERR_DTYPE;
+  if (s->kernel < TRIFAST_KERNEL_AUTO || s->kernel > TRIFAST_KERNEL_TCGEN05)
+    return TRIFAST_ERR_KERNEL_CHOICE;
+  return TRIFAST_OK;
+}
+
+// Row-vector tensors are read with 16-byte vector / TMA accesses by the
+// tensor-core kernels, so bases are 16-byte aligned and every stride is a
+// whole number of 16-byte units for all kernels alike.
+int check_t5(const trifast_t5* t, const trifast_shape* s) {
+  if (!t || !t->data) return TRIFAST_ERR_NULL;
+  if (((uintptr_t)t->data) & 15) return TRIFAST_ERR_ALIGN;
+  const int eb = elem_bytes(s->dtype);
+  for (int a = 0; a < 4; ++a) {
+    if (t->stride[a] < 0) return TRIFAST_ERR_STRIDE;
+    if ((t->stride[a] * eb) & 15) return TRIFAST_ERR_STRIDE;
+  }
+  if (t->stride[3] < s->d) return TRIFAST_ERR_STRIDE;
+  return TRIFAST_OK;
+}
+
+int check_t4(const trifast_t4* t, const trifast_shape* s) {
+  if (!t || !t->data) return TRIFAST_ERR_NULL;
+  const int eb = elem_bytes(s->dtype);
+  if (((uintptr_t)t->data) & (eb - 1)) return TRIFAST_ERR_ALIGN;
+  for (int a = 0; a < 3; ++a)
+    if (t->stride[a] < 0) return TRIFAST_ERR_STRIDE;
+  if (t->stride[2] < s->n) return TRIFAST_ERR_STRIDE;
+  return TRIFAST_OK;
+}
+
+int check_mask(const trifast_mask* m, const trifast_shape* s) {
+  if (!m || !m->data) return TRIFAST_ERR_NULL;
+  if (m->stride[0] < 0 || m->stride[1] < s->n) return TRIFAST_ERR_STRIDE;
+  return TRIFAST_OK;
+}
+
+Dims make_dims(const trifast_shape* s) {
+  Dims dm;
+  dm.batch = s->batch;
+  dm.heads = s->heads;
+  dm.n = s->n;
+  dm.n_rows = s->n_rows;
+  dm.d = s->d;
+  dm.scale = 1.0f / sqrtf((float)s->d);
+  dm.sentinel = dtype_sentinel(s->dtype);
+  return dm;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Carve-up of the backward workspace.
+struct Workspace {
+  size_t delta_off, rowfull_off, db_off, partial_off, total;
+};
+
+Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
+  Workspace w;
+  const size_t stat = (size_t)s->batch * s->heads * s->n_rows * s->n * sizeof(float);
+  const size_t dbb = (size_t)s->batch * s->heads * s->n * s->n * sizeof(float);
+  size_t off = 0;
+  w.delta_off = off;
+  off = align_up(off + stat, 256);
+  w.rowfull_off = off;
+  off = align_up(off + (size_t)s->batch * s->n_rows, 256);
+  w.db_off = off;
+  off = align_up(off + dbb, 256);
+  w.partial_off = off;
+  if (plan.db_row_splits > 1) off = align_up(off + dbb * plan.db_row_splits, 256);
+  w.total = off;
+  return w;
+}
+
+int pick_plan(const trifast_shape* s, trifast_plan* p) {
+  int rc = check_shape(s);
+  if (rc) return rc;
+  *p = trifast_plan{};
+  const bool half = s->dtype != TRIFAST_F32;
+  // tcgen05 path: 16-bit inputs, d in {32, 64}; the bias tile comes through TMA,
+  // whose row pitch must be a multiple of 16 bytes (n % 8 == 0), and problems
+  // smaller than one 128-wide tile gain nothing from it.
+  const bool tc_ok = half && (s->d == 32 || s->d == 64) && (s->n % 8 == 0) && s->n >= 128;
+  int kernel = s->kernel;
+  if (kernel == TRIFAST_KERNEL_AUTO) kernel = tc_ok ? TRIFAST_KERNEL_TCGEN05 : TRIFAST_KERNEL_SIMT;
+  if (kernel == TRIFAST_KERNEL_TCGEN05 && !tc_ok) return TRIFAST_ERR_KERNEL_CHOICE;
+  p->kernel = kernel;
+  if (kernel == TRIFAST_KERNEL_TCGEN05) {
+    p->block_j = 128;
+    p->block_k = 128;
+    p->rows_per_cta = 2;
+    p->stages = (s->d == 32) ? 3 : 2;
+  } else {
+    p->block_j = 64;
+    p->block_k = (s->d <= 32) ? 32 : 16;
+    p->rows_per_cta = 1;
+    p->stages = 1;
+  }
+  // db: CTAs = tiles * splits.  Split the local rows until the grid covers the
+  // 148 SMs about twice, but never below 8 rows per split and at most 16 splits.
+  const int tile = 32;
+  const int64_t t = (s->n + tile - 1) / tile;
+  const int64_t tiles = t * t * s->batch * s->heads;
+  int splits = 1;
+  while (splits < 16 && tiles * splits < 296 && s->n_rows / (splits * 2) >= 8) splits *= 2;
+  p->db_row_splits = splits;
+  return TRIFAST_OK;
+}
+
+struct Common {
+  Dims dm;
+  trifast_plan plan;
+  unsigned int* status;
+};
+
+int common_setup(const trifast_shape* s, Common* c) {
+  int rc = pick_plan(s, &c->plan);
+  if (rc) return rc;
+  int dev;
+  rc = device_setup(&dev, &c->status);
+  if (rc) return rc;
+  c->dm = make_dims(s);
+  return TRIFAST_OK;
+}
+
+int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
+             const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+             const trifast_t4* bias, const trifast_mask* mask, const trifast_t5* o,
+             const float* lse, void* workspace, size_t workspace_bytes, BwdArgs* a) {
+  int rc;
+  if ((rc = check_t5(d_o, shape)) || (rc = check_t5(q, shape)) || (rc = check_t5(k, shape)) ||
+      (rc = check_t5(v, shape)) || (rc = check_t4(bias, shape)) || (rc = check_mask(mask, shape)))
+    return rc;
+  if (o && (rc = check_t5(o, shape))) return rc;
+  if (!lse) return TRIFAST_ERR_NULL;
+  const Workspace w = carve(shape, c.plan);
+  if (!workspace || workspace_bytes < w.total) return TRIFAST_ERR_WORKSPACE;
+  if (((uintptr_t)workspace) & 255) return TRIFAST_ERR_ALIGN;
+  *a = BwdArgs{};
+  a->d_o = make_view(d_o);
+  a->q = make_view(q);
+  a->k = make_view(k);
+  a->v = make_view(v);
+  if (o) a->o = make_view(o);
+  a->bias = make_view(bias);
+  a->mask = make_view(mask);
+  a->lse = lse;
+  char* base = (char*)workspace;
+  a->delta = (float*)(base + w.delta_off);
+  a->rowfull = (uint8_t*)(base + w.rowfull_off);
+  a->db_f32 = (float*)(base + w.db_off);
+  a->db_partials = (float*)(base + w.partial_off);
+  a->splits = c.plan.db_row_splits;
+  a->dm = c.dm;
+  a->dtype = shape->dtype;
+  a->status = c.status;
+  return TRIFAST_OK;
+}
+
+int cuda_rc(cudaError_t e) { return e == cudaSuccess ? TRIFAST_OK : TRIFAST_ERR_LAUNCH; }
+
+}  // namespace
+}  // namespace trifast
+
+using namespace trifast;
+
+extern "C" {
+
+int trifast_version(void) { return 100; }
+
+const char* trifast_status_str(int status) {
+  switch (status) {
+    case TRIFAST_OK: return "ok";
+    case TRIFAST_ERR_NULL: return "a required pointer is NULL";
+    case TRIFAST_ERR_SHAPE: return "invalid shape (extents must be positive, n_rows <= n, batch*heads and n_rows <= 65535)";
+    case TRIFAST_ERR_HEAD_DIM: return "head dim must be 16, 32, 64 or 128";
+    case TRIFAST_ERR_DTYPE: return "dtype must be fp32, bf16 or fp16";
+    case TRIFAST_ERR_STRIDE: return "invalid stride (negative, overlapping, or not a multiple of 16 bytes)";
+    case TRIFAST_ERR_ALIGN: return "pointer is not sufficiently aligned (16 bytes for q/k/v/o and gradients, 256 for the workspace)";
+    case TRIFAST_ERR_WORKSPACE: return "workspace is NULL or smaller than trifast_backward_workspace_bytes()";
+    case TRIFAST_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+    case TRIFAST_ERR_LAUNCH: return "CUDA reported an error at launch";
+    case TRIFAST_ERR_KERNEL_CHOICE: return "the requested kernel family cannot run this problem";
+    case TRIFAST_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+    case TRIFAST_ERR_TOO_LARGE: return "problem is larger than this entry point's stated maximum";
+    default: return "unknown status";
+  }
+}
+
+int trifast_pick_plan(const trifast_shape* shape, trifast_plan* plan) {
+  if (!plan) return TRIFAST_ERR_NULL;
+  return pick_plan(shape, plan);
+}
+
+size_t trifast_backward_workspace_bytes(const trifast_shape* shape) {
+  trifast_plan plan;
+  if (pick_plan(shape, &plan)) return 0;
+  return carve(shape, plan).total;
+}
+
+int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifast_t5* k,
+                    const trifast_t5* v, const trifast_t4* bias, const trifast_mask* mask,
+                    const trifast_t5* o, float* lse, void* stream) {
+  int rc = check_shape(shape);
+  if (rc) return rc;
+  if ((rc = check_t5(q, shape)) || (rc = check_t5(k, shape)) || (rc = check_t5(v, shape)) ||
+      (rc = check_t5(o, shape)) || (rc = check_t4(bias, shape)) || (rc = check_mask(mask, shape)))
+    return rc;
+  if (!lse) return TRIFAST_ERR_NULL;
+  Common c;
+  if ((rc = common_setup(shape, &c))) return rc;
+  FwdArgs a{};
+  a.q = make_view(q);
+  a.k = make_view(k);
+  a.v = make_view(v);
+  a.o = make_view(o);
+  a.bias = make_view(bias);
+  a.mask = make_view(mask);
+  a.lse = lse;
+  a.dm = c.dm;
+  a.dtype = shape->dtype;
+  a.status = c.status;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c.plan.kernel == TRIFAST_KERNEL_TCGEN05) {
+    if (!tc_forward_supported(c.dm, shape->dtype, &a)) {
+      if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
+      return cuda_rc(simt_forward(a, s));
+    }
+    return cuda_rc(tc_forward(a, c.plan, s));
+  }
+  return cuda_rc(simt_forward(a, s));
+}
+
+int trifast_backward_db(const trifast_shape* shape, const trifast_t5* d_o, const trifast_t5* q,
+                        const trifast_t5* k, const trifast_t5* v, const trifast_t4* bias,
+                        const trifast_mask* mask, const trifast_t5* o, const float* lse,
+                        float* db_f32, void* workspace, size_t workspace_bytes, void* stream) {
+  Common c;
+  int rc = common_setup(shape, &c);
+  if (rc) return rc;
+  if (!o || !db_f32) return TRIFAST_ERR_NULL;
+  BwdArgs a;
+  if ((rc = fill_bwd(shape, c, d_o, q, k, v, bias, mask, o, lse, workspace, workspace_bytes, &a)))
+    return rc;
+  a.db_f32 = db_f32;
+  cudaStream_t s = (cudaStream_t)stream;
+  if ((rc = cuda_rc(bwd_prepare(a, s)))) return rc;
+  if ((rc = cuda_rc(simt_bwd_db(a, s)))) return rc;
+  return cuda_rc(db_reduce_splits(a, s));
+}
+
+int trifast_backward_dqkv(const trifast_shape* shape, const trifast_t5* d_o, const trifast_t5* q,
+                          const trifast_t5* k, const trifast_t5* v, const trifast_t4* bias,
+                          const trifast_mask* mask, const float* lse, const trifast_t5* dq,
+                          const trifast_t5* dk, const trifast_t5* dv, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  Common c;
+  int rc = common_setup(shape, &c);
+  if (rc) return rc;
+  if ((rc = check_t5(dq, shape)) || (rc = check_t5(dk, shape)) || (rc = check_t5(dv, shape)))
+    return rc;
+  BwdArgs a;
+  if ((rc = fill_bwd(shape, c, d_o, q, k, v, bias, mask, nullptr, lse, workspace,
+                     workspace_bytes, &a)))
+    return rc;
+  a.dq = make_view(dq);
+  a.dk = make_view(dk);
+  a.dv = make_view(dv);
+  return cuda_rc(simt_bwd_dqkv(a, (cudaStream_t)stream));
+}
+
+int trifast_db_finalize(const trifast_shape* shape, const float* db_f32, const trifast_t4* db,
+                        void* stream) {
+  int rc = check_shape(shape);
+  if (rc) return rc;
+  if (!db_f32) return TRIFAST_ERR_NULL;
+  if ((rc = check_t4(db, shape))) return rc;
+  return cuda_rc(db_cast(db_f32, make_view(db), shape->dtype, shape->batch, shape->heads,
+                         shape->n, (cudaStream_t)stream));
+}
+
+int trifast_backward(const trifast_shape* shape, const trifast_t5* d_o, const trifast_t5* q,
+                     const trifast_t5* k, const trifast_t5* v, const trifast_t4* bias,
+                     const trifast_mask* mask, const trifast_t5* o, const float* lse,
+                     const trifast_t5* dq, const trifast_t5* dk, const trifast_t5* dv,
+                     const trifast_t4* db, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  int rc = check_shape(shape);
+  if (rc) return rc;
+  trifast_plan plan;
+  if ((rc = pick_plan(shape, &plan))) return rc;
+  const Workspace w = carve(shape, plan);
+  if (!workspace || workspace_bytes < w.total) return TRIFAST_ERR_WORKSPACE;
+  float* db_f32 = (float*)((char*)workspace + w.db_off);
+  if ((rc = trifast_backward_db(shape, d_o, q, k, v, bias, mask, o, lse, db_f32, workspace,
+                                workspace_bytes, stream)))
+    return rc;
+  if ((rc = trifast_backward_dqkv(shape, d_o, q, k, v, bias, mask, lse, dq, dk, dv, workspace,
+                                  workspace_bytes, stream)))
+    return rc;
+  return trifast_db_finalize(shape, db_f32, db, stream);
+}
+
+int trifast_check_device_status(void* stream) {
+  int dev;
+  unsigned int* status;
+  int rc = device_setup(&dev, &status);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned int host = 0;
+  if (cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return TRIFAST_ERR_LAUNCH;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return TRIFAST_ERR_LAUNCH;
+  if (host == 0) return TRIFAST_OK;
+  cudaMemsetAsync(status, 0, sizeof(host), s);
+  cudaStreamSynchronize(s);
+  return TRIFAST_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,555 @@
+// CUDA-core (fp32 accumulate, fp32 softmax) triangle-attention kernels.
+//
+// They serve every dtype, every n (ragged included) and d in {16, 32, 64, 128}:
+// the fp32 contract (1e-4 relative to the fp32 reference cannot be met through
+// tensor cores without operand splitting) and the shapes the tcgen05 kernels do
+// not take.  Structure per kernel:
+//   forward : one thread per query j of a (b, h, i, j-tile); K/V tiles staged in
+//             shared memory and read as broadcasts; online softmax per key tile.
+//   dq      : same mapping; recomputes P from lse, dS = P * (dP - delta).
+//   dk/dv   : one thread per key k of a (b, h, i, k-tile); Q/dO tiles broadcast.
+//   db      : one CTA per (b, h, 32x32 (j,k) tile, row split); loops over its rows
+//             and sums dS in registers -> fixed-order reduction, no atomics.
+// Semantics follow the reference's PyTorch path (src/trifast/equiv.py:42-69):
+// masked keys weigh exactly 0; a row whose keys are all masked gets uniform
+// weights 1/n in the forward and in the backward.
+
+#include <math.h>
+
+#include <type_traits>
+
+#include "kernels.h"
+
+namespace trifast {
+namespace {
+
+constexpr float kMinusInf = -INFINITY;
+constexpr float kMaxInit = -1e30f;  // finite start of the running max: exp(-inf - m) stays 0, never NaN
+
+template <typename T>
+__device__ __forceinline__ const T* row5(const View5& t, int b, int h, int i, int j) {
+  return (const T*)t.p + b * t.sb + h * t.sh + (int64_t)i * t.si + (int64_t)j * t.sj;
+}
+template <typename T>
+__device__ __forceinline__ T* row5w(const View5& t, int b, int h, int i, int j) {
+  return (T*)t.p + b * t.sb + h * t.sh + (int64_t)i * t.si + (int64_t)j * t.sj;
+}
+template <typename T>
+__device__ __forceinline__ const T* row4(const View4& t, int b, int h, int j) {
+  return (const T*)t.p + b * t.sb + h * t.sh + (int64_t)j * t.sj;
+}
+
+// Stage `rows` x D elements (row r at src(r)) into shared memory as fp32; rows
+// beyond `valid` are zero.  Consecutive threads read consecutive elements.
+template <typename T, int D, int ROWS, int NT, typename RowFn>
+__device__ __forceinline__ void stage_tile(float (*dst)[D], int valid, RowFn src) {
+  for (int idx = threadIdx.x; idx < ROWS * D; idx += NT) {
+    const int r = idx / D, c = idx % D;
+    dst[r][c] = (r < valid) ? to_f32<T>(src(r)[c]) : 0.f;
+  }
+}
+
+template <int D>
+__device__ __forceinline__ float dot_smem(const float* reg, const float* sm) {
+  float acc = 0.f;
+  const float4* s4 = reinterpret_cast<const float4*>(sm);
+#pragma unroll
+  for (int c = 0; c < D / 4; ++c) {
+    const float4 x = s4[c];
+    acc = fmaf(reg[4 * c + 0], x.x, acc);
+    acc = fmaf(reg[4 * c + 1], x.y, acc);
+    acc = fmaf(reg[4 * c + 2], x.z, acc);
+    acc = fmaf(reg[4 * c + 3], x.w, acc);
+  }
+  return acc;
+}
+
+template <int D>
+__device__ __forceinline__ void axpy_smem(float a, const float* sm, float* reg) {
+  const float4* s4 = reinterpret_cast<const float4*>(sm);
+#pragma unroll
+  for (int c = 0; c < D / 4; ++c) {
+    const float4 x = s4[c];
+    reg[4 * c + 0] = fmaf(a, x.x, reg[4 * c + 0]);
+    reg[4 * c + 1] = fmaf(a, x.y, reg[4 * c + 1]);
+    reg[4 * c + 2] = fmaf(a, x.z, reg[4 * c + 2]);
+    reg[4 * c + 3] = fmaf(a, x.w, reg[4 * c + 3]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// rowfull[b, i] = 1 when every key of pair row i is masked.
+// ---------------------------------------------------------------------------
+__global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowfull) {
+  const int bi = blockIdx.x;
+  const int b = bi / n_rows, i = bi % n_rows;
+  const uint8_t* row = mask.p + b * mask.sb + (int64_t)i * mask.si;
+  int open = 0;
+  for (int k = threadIdx.x; k < n; k += blockDim.x) open |= (row[k] == 0);
+  open = __syncthreads_or(open);
+  if (threadIdx.x == 0) rowfull[bi] = open ? 0 : 1;
+}
+
+// ---------------------------------------------------------------------------
+// delta[b, h, i, j] = sum_d o * dO   (fp32; never rounded to the input dtype)
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void delta_kernel(View5 o, View5 d_o, float* delta, Dims dm) {
+  const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int j = idx % dm.n;
+  int64_t r = idx / dm.n;
+  const int i = r % dm.n_rows;
+  r /= dm.n_rows;
+  const int h = r % dm.heads, b = r / dm.heads;
+  const T* po = row5<T>(o, b, h, i, j);
+  const T* pd = row5<T>(d_o, b, h, i, j);
+  float acc = 0.f;
+#pragma unroll
+  for (int c = 0; c < D; ++c) acc = fmaf(to_f32<T>(po[c]), to_f32<T>(pd[c]), acc);
+  delta[idx] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------
+template <typename T, int D, int BJ, int BK>
+__global__ void __launch_bounds__(BJ) simt_fwd_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                      MaskView mask, View5 o, float* lse,
+                                                      Dims dm) {
+  __shared__ __align__(16) float Ks[BK][D];
+  __shared__ __align__(16) float Vs[BK][D];
+  __shared__ uint8_t Ms[BK];
+  const int n = dm.n;
+  const int i = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x;
+  const int j = blockIdx.x * BJ + tid;
+  const bool jvalid = j < n;
+
+  const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+  int open = 0;
+  for (int kk = tid; kk < n; kk += BJ) open |= (mrow[kk] == 0);
+  const bool row_full = !__syncthreads_or(open);
+
+  float qr[D], acc[D];
+#pragma unroll
+  for (int c = 0; c < D; ++c) acc[c] = 0.f;
+  {
+    const T* pq = row5<T>(q, b, h, i, jvalid ? j : 0);
+#pragma unroll
+    for (int c = 0; c < D; ++c) qr[c] = jvalid ? to_f32<T>(pq[c]) : 0.f;
+  }
+  const T* brow = row4<T>(bias, b, h, jvalid ? j : 0);
+  float m = kMaxInit, l = 0.f;
+
+  for (int k0 = 0; k0 < n; k0 += BK) {
+    __syncthreads();
+    const int valid = min(BK, n - k0);
+    stage_tile<T, D, BK, BJ>(Ks, valid, [&](int r) { return row5<T>(k, b, h, i, k0 + r); });
+    stage_tile<T, D, BK, BJ>(Vs, valid, [&](int r) { return row5<T>(v, b, h, i, k0 + r); });
+    for (int t = tid; t < BK; t += BJ) Ms[t] = (t < valid) ? (row_full ? 0 : mrow[k0 + t]) : 1;
+    __syncthreads();
+
+    float sc[BK];
+    float mt = kMinusInf;
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float x = dot_smem<D>(qr, Ks[kk]);
+      const float bv = (kk < valid && jvalid) ? to_f32<T>(brow[k0 + kk]) : 0.f;
+      x = row_full ? 0.f : fmaf(x, dm.scale, bv);
+      if (Ms[kk]) x = kMinusInf;
+      sc[kk] = x;
+      mt = fmaxf(mt, x);
+    }
+    const float m_new = fmaxf(m, mt);
+    const float alpha = expf(m - m_new);
+    l *= alpha;
+#pragma unroll
+    for (int c = 0; c < D; ++c) acc[c] *= alpha;
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      const float p = expf(sc[kk] - m_new);
+      l += p;
+      axpy_smem<D>(p, Vs[kk], acc);
+    }
+    m = m_new;
+  }
+  if (jvalid) {
+    const float inv = 1.f / l;
+    T* po = row5w<T>(o, b, h, i, j);
+#pragma unroll
+    for (int c = 0; c < D; ++c) po[c] = from_f32<T>(acc[c] * inv);
+    lse[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + j] =
+        row_full ? dm.sentinel : m + logf(l);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dq: thread per query j.
+// ---------------------------------------------------------------------------
+template <typename T, int D, int BJ, int BK>
+__global__ void __launch_bounds__(BJ) simt_dq_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                     MaskView mask, View5 d_o, View5 dq,
+                                                     const float* lse, const float* delta,
+                                                     const uint8_t* rowfull, Dims dm) {
+  __shared__ __align__(16) float Ks[BK][D];
+  __shared__ __align__(16) float Vs[BK][D];
+  __shared__ uint8_t Ms[BK];
+  const int n = dm.n;
+  const int i = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x;
+  const int j = blockIdx.x * BJ + tid;
+  const bool jvalid = j < n;
+  const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+  const float uniform = 1.f / (float)n;
+  const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+
+  float qr[D], gr[D], acc[D];
+  {
+    const T* pq = row5<T>(q, b, h, i, jvalid ? j : 0);
+    const T* pg = row5<T>(d_o, b, h, i, jvalid ? j : 0);
+#pragma unroll
+    for (int c = 0; c < D; ++c) {
+      qr[c] = jvalid ? to_f32<T>(pq[c]) : 0.f;
+      gr[c] = jvalid ? to_f32<T>(pg[c]) : 0.f;
+      acc[c] = 0.f;
+    }
+  }
+  const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + (jvalid ? j : 0);
+  const float my_lse = lse[stat], my_delta = delta[stat];
+  const T* brow = row4<T>(bias, b, h, jvalid ? j : 0);
+
+  for (int k0 = 0; k0 < n; k0 += BK) {
+    __syncthreads();
+    const int valid = min(BK, n - k0);
+    stage_tile<T, D, BK, BJ>(Ks, valid, [&](int r) { return row5<T>(k, b, h, i, k0 + r); });
+    stage_tile<T, D, BK, BJ>(Vs, valid, [&](int r) { return row5<T>(v, b, h, i, k0 + r); });
+    for (int t = tid; t < BK; t += BJ) Ms[t] = (t < valid) ? (row_full ? 0 : mrow[k0 + t]) : 1;
+    __syncthreads();
+#pragma unroll 4
+    for (int kk = 0; kk < BK; ++kk) {
+      float p;
+      if (Ms[kk]) {
+        p = 0.f;
+      } else if (row_full) {
+        p = uniform;
+      } else {
+        const float s = dot_smem<D>(qr, Ks[kk]);
+        const float bv = jvalid ? to_f32<T>(brow[k0 + kk]) : 0.f;
+        p = expf(fmaf(s, dm.scale, bv) - my_lse);
+      }
+      const float dp = dot_smem<D>(gr, Vs[kk]);
+      const float ds = p * (dp - my_delta);
+      axpy_smem<D>(ds, Ks[kk], acc);
+    }
+  }
+  if (jvalid) {
+    T* pdq = row5w<T>(dq, b, h, i, j);
+#pragma unroll
+    for (int c = 0; c < D; ++c) pdq[c] = from_f32<T>(acc[c] * dm.scale);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dk, dv: thread per key k.
+// ---------------------------------------------------------------------------
+template <typename T, int D, int BKT, int BJT>
+__global__ void __launch_bounds__(BKT) simt_dkv_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                       MaskView mask, View5 d_o, View5 dk,
+                                                       View5 dv, const float* lse,
+                                                       const float* delta,
+                                                       const uint8_t* rowfull, Dims dm) {
+  __shared__ __align__(16) float Qs[BJT][D];
+  __shared__ __align__(16) float Gs[BJT][D];
+  __shared__ float Ls[BJT], Ds[BJT];
+  const int n = dm.n;
+  const int i = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x;
+  const int key = blockIdx.x * BKT + tid;
+  const bool kvalid = key < n;
+  const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+  const float uniform = 1.f / (float)n;
+  const bool masked =
+      !kvalid || (!row_full && mask.p[b * mask.sb + (int64_t)i * mask.si + key] != 0);
+
+  float kr[D], vr[D], acck[D], accv[D];
+  {
+    const T* pk = row5<T>(k, b, h, i, kvalid ? key : 0);
+    const T* pv = row5<T>(v, b, h, i, kvalid ? key : 0);
+#pragma unroll
+    for (int c = 0; c < D; ++c) {
+      kr[c] = kvalid ? to_f32<T>(pk[c]) : 0.f;
+      vr[c] = kvalid ? to_f32<T>(pv[c]) : 0.f;
+      acck[c] = 0.f;
+      accv[c] = 0.f;
+    }
+  }
+  const int64_t stat0 = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n;
+
+  for (int j0 = 0; j0 < n; j0 += BJT) {
+    __syncthreads();
+    const int valid = min(BJT, n - j0);
+    stage_tile<T, D, BJT, BKT>(Qs, valid, [&](int r) { return row5<T>(q, b, h, i, j0 + r); });
+    stage_tile<T, D, BJT, BKT>(Gs, valid, [&](int r) { return row5<T>(d_o, b, h, i, j0 + r); });
+    for (int t = tid; t < BJT; t += BKT) {
+      Ls[t] = (t < valid) ? lse[stat0 + j0 + t] : 0.f;
+      Ds[t] = (t < valid) ? delta[stat0 + j0 + t] : 0.f;
+    }
+    __syncthreads();
+    if (masked) continue;  // exactly zero weight: no contribution to dk, dv
+    for (int jj = 0; jj < valid; ++jj) {
+      float p;
+      if (row_full) {
+        p = uniform;
+      } else {
+        const float s = dot_smem<D>(kr, Qs[jj]);
+        const float bv = to_f32<T>(row4<T>(bias, b, h, j0 + jj)[key]);
+        p = expf(fmaf(s, dm.scale, bv) - Ls[jj]);
+      }
+      const float dp = dot_smem<D>(vr, Gs[jj]);
+      const float ds = p * (dp - Ds[jj]);
+      axpy_smem<D>(p, Gs[jj], accv);
+      axpy_smem<D>(ds, Qs[jj], acck);
+    }
+  }
+  if (kvalid) {
+    T* pdk = row5w<T>(dk, b, h, i, key);
+    T* pdv = row5w<T>(dv, b, h, i, key);
+#pragma unroll
+    for (int c = 0; c < D; ++c) {
+      pdk[c] = from_f32<T>(acck[c] * dm.scale);
+      pdv[c] = from_f32<T>(accv[c]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// db partials: CTA = (32 x 32 (j, k) tile, row split); 256 threads, 2 x 2 each.
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256) simt_db_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                      MaskView mask, View5 d_o,
+                                                      const float* lse, const float* delta,
+                                                      const uint8_t* rowfull, float* out,
+                                                      int splits, Dims dm) {
+  // The head dim is staged in chunks of DC so the four tiles fit static shared memory.
+  constexpr int TJ = 32, TK = 32, DC = (D > 64) ? 64 : D, P = DC + 1;  // +1: conflict-free row reads
+  __shared__ float Qs[TJ][P], Gs[TJ][P], Ks[TK][P], Vs[TK][P];
+  __shared__ float Ls[TJ], Ds[TJ];
+  __shared__ uint8_t Ms[TK];
+  const int n = dm.n;
+  const int tiles_k = (n + TK - 1) / TK;
+  const int jt = blockIdx.x / tiles_k, kt = blockIdx.x % tiles_k;
+  const int split = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x;
+  const int tj = (tid / 16) * 2, tk = (tid % 16) * 2;  // my 2 x 2 corner
+  const int j0 = jt * TJ, k0 = kt * TK;
+  const int vj = min(TJ, n - j0), vk = min(TK, n - k0);
+  const float uniform = 1.f / (float)n;
+
+  float bv[2][2], acc[2][2];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int j = j0 + tj + a, key = k0 + tk + c;
+      bv[a][c] = (j < n && key < n) ? to_f32<T>(row4<T>(bias, b, h, j)[key]) : 0.f;
+      acc[a][c] = 0.f;
+    }
+
+  // Rows of this split: a contiguous block, the same partition for every tile.
+  const int per = (dm.n_rows + splits - 1) / splits;
+  const int i_begin = split * per, i_end = min(dm.n_rows, i_begin + per);
+
+  for (int i = i_begin; i < i_end; ++i) {
+    const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+    const int64_t stat0 = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n;
+    float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, dp[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    for (int c0 = 0; c0 < D; c0 += DC) {
+      __syncthreads();
+      for (int idx = tid; idx < TJ * DC; idx += 256) {
+        const int r = idx / DC, c = idx % DC;
+        const bool ok = r < vj;
+        Qs[r][c] = ok ? to_f32<T>(row5<T>(q, b, h, i, j0 + r)[c0 + c]) : 0.f;
+        Gs[r][c] = ok ? to_f32<T>(row5<T>(d_o, b, h, i, j0 + r)[c0 + c]) : 0.f;
+      }
+      for (int idx = tid; idx < TK * DC; idx += 256) {
+        const int r = idx / DC, c = idx % DC;
+        const bool ok = r < vk;
+        Ks[r][c] = ok ? to_f32<T>(row5<T>(k, b, h, i, k0 + r)[c0 + c]) : 0.f;
+        Vs[r][c] = ok ? to_f32<T>(row5<T>(v, b, h, i, k0 + r)[c0 + c]) : 0.f;
+      }
+      if (c0 == 0) {
+        if (tid < TJ) {
+          Ls[tid] = (tid < vj) ? lse[stat0 + j0 + tid] : 0.f;
+          Ds[tid] = (tid < vj) ? delta[stat0 + j0 + tid] : 0.f;
+        } else if (tid < TJ + TK) {
+          const int t = tid - TJ;
+          Ms[t] = (t < vk) ? (row_full ? 0 : mask.p[b * mask.sb + (int64_t)i * mask.si + k0 + t]) : 1;
+        }
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int c = 0; c < DC; ++c) {
+        const float q0 = Qs[tj][c], q1 = Qs[tj + 1][c], g0 = Gs[tj][c], g1 = Gs[tj + 1][c];
+        const float x0 = Ks[tk][c], x1 = Ks[tk + 1][c], y0 = Vs[tk][c], y1 = Vs[tk + 1][c];
+        s[0][0] = fmaf(q0, x0, s[0][0]);
+        s[0][1] = fmaf(q0, x1, s[0][1]);
+        s[1][0] = fmaf(q1, x0, s[1][0]);
+        s[1][1] = fmaf(q1, x1, s[1][1]);
+        dp[0][0] = fmaf(g0, y0, dp[0][0]);
+        dp[0][1] = fmaf(g0, y1, dp[0][1]);
+        dp[1][0] = fmaf(g1, y0, dp[1][0]);
+        dp[1][1] = fmaf(g1, y1, dp[1][1]);
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float p;
+        if (Ms[tk + c] || tj + a >= vj) {
+          p = 0.f;
+        } else if (row_full) {
+          p = uniform;
+        } else {
+          p = expf(fmaf(s[a][c], dm.scale, bv[a][c]) - Ls[tj + a]);
+        }
+        acc[a][c] += p * (dp[a][c] - Ds[tj + a]);
+      }
+  }
+  float* dst = out + ((int64_t)split * dm.batch * dm.heads + bh) * n * n;
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int j = j0 + tj + a, key = k0 + tk + c;
+      if (j < n && key < n) dst[(int64_t)j * n + key] = acc[a][c];
+    }
+}
+
+// Sum the row-split partials in split order (fixed order => deterministic).
+__global__ void db_reduce_kernel(const float* partials, float* out, int splits, int64_t count) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count) return;
+  float acc = partials[idx];
+  for (int s = 1; s < splits; ++s) acc += partials[(int64_t)s * count + idx];
+  out[idx] = acc;
+}
+
+template <typename T>
+__global__ void db_cast_kernel(const float* src, View4 db, int heads, int n, int64_t count) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count) return;
+  const int key = idx % n;
+  int64_t r = idx / n;
+  const int j = r % n;
+  r /= n;
+  const int h = r % heads, b = r / heads;
+  T* dst = (T*)db.p + b * db.sb + h * db.sh + (int64_t)j * db.sj;
+  dst[key] = from_f32<T>(src[idx]);
+}
+
+// ---------------------------------------------------------------------------
+// dispatch on (dtype, d)
+// ---------------------------------------------------------------------------
+template <typename F>
+cudaError_t dispatch(int dtype, int d, F&& f) {
+#define TRIFAST_D_CASES(T)                                 \
+  switch (d) {                                             \
+    case 16: f((T*)nullptr, std::integral_constant<int, 16>{}); break;   \
+    case 32: f((T*)nullptr, std::integral_constant<int, 32>{}); break;   \
+    case 64: f((T*)nullptr, std::integral_constant<int, 64>{}); break;   \
+    case 128: f((T*)nullptr, std::integral_constant<int, 128>{}); break; \
+    default: return cudaErrorInvalidValue;                 \
+  }
+  switch (dtype) {
+    case TRIFAST_F32: TRIFAST_D_CASES(float) break;
+    case TRIFAST_BF16: TRIFAST_D_CASES(__nv_bfloat16) break;
+    case TRIFAST_F16: TRIFAST_D_CASES(__half) break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef TRIFAST_D_CASES
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    constexpr int D = decltype(dc)::value;
+    constexpr int BJ = 64, BK = (D <= 32) ? 32 : 16;
+    dim3 grid((dm.n + BJ - 1) / BJ, dm.n_rows, dm.batch * dm.heads);
+    simt_fwd_kernel<T, D, BJ, BK><<<grid, BJ, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.o, a.lse, dm);
+  });
+}
+
+cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull);
+  return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    constexpr int D = decltype(dc)::value;
+    const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
+    delta_kernel<T, D><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(a.o, a.d_o, a.delta, dm);
+  });
+}
+
+cudaError_t simt_bwd_db(const BwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    constexpr int D = decltype(dc)::value;
+    const int t = (dm.n + 31) / 32;
+    dim3 grid(t * t, a.splits, dm.batch * dm.heads);
+    float* out = a.splits > 1 ? a.db_partials : a.db_f32;
+    simt_db_kernel<T, D><<<grid, 256, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.lse,
+                                              a.delta, a.rowfull, out, a.splits, dm);
+  });
+}
+
+cudaError_t db_reduce_splits(const BwdArgs& a, cudaStream_t s) {
+  if (a.splits <= 1) return cudaSuccess;
+  const int64_t count = (int64_t)a.dm.batch * a.dm.heads * a.dm.n * a.dm.n;
+  db_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(a.db_partials, a.db_f32,
+                                                                 a.splits, count);
+  return cudaGetLastError();
+}
+
+cudaError_t simt_bwd_dqkv(const BwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    constexpr int D = decltype(dc)::value;
+    constexpr int BJ = 64, BK = (D <= 32) ? 32 : 16;
+    dim3 gq((dm.n + BJ - 1) / BJ, dm.n_rows, dm.batch * dm.heads);
+    simt_dq_kernel<T, D, BJ, BK><<<gq, BJ, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.dq,
+                                                   a.lse, a.delta, a.rowfull, dm);
+    constexpr int BKT = 64, BJT = (D <= 32) ? 32 : 16;
+    dim3 gk((dm.n + BKT - 1) / BKT, dm.n_rows, dm.batch * dm.heads);
+    simt_dkv_kernel<T, D, BKT, BJT><<<gk, BKT, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o,
+                                                       a.dk, a.dv, a.lse, a.delta, a.rowfull, dm);
+  });
+}
+
+cudaError_t db_cast(const float* db_f32, View4 db, int dtype, int batch, int heads, int n,
+                    cudaStream_t s) {
+  const int64_t count = (int64_t)batch * heads * n * n;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  switch (dtype) {
+    case TRIFAST_F32: db_cast_kernel<float><<<blocks, 256, 0, s>>>(db_f32, db, heads, n, count); break;
+    case TRIFAST_BF16: db_cast_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(db_f32, db, heads, n, count); break;
+    case TRIFAST_F16: db_cast_kernel<__half><<<blocks, 256, 0, s>>>(db_f32, db, heads, n, count); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace trifast
