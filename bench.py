@@ -1,0 +1,428 @@
+"""Benchmark of the triangle-attention hot path (forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step = one forward + backward of the workload (default: the headline shape
+n = 1024, h = 4, d = 32, bf16, batch 1, nothing masked) on synthetic, seeded
+inputs.  With N > 1 (launched under torchrun, one rank per GPU) the pair rows of
+that one problem are sharded over the ranks (strong scaling) and the step
+includes the NCCL all-reduce of the bias gradient.  Rank 0 prints ONE JSON line.
+
+Keys beyond the usual ones:
+  value / ms_per_step : kernels only, inputs resident in HBM, CUDA events, max over ranks
+  e2e                 : the same step through the public autograd API with pinned-host
+                        inputs copied in and o, dq, dk, dv, db copied out every step
+  roofline            : the dominant kernel phase against the measured bf16 tensor peak
+  phases_ms           : forward / db / dq+dk+dv phase times (CUDA events, N = 1)
+  cpu_baseline        : the PyTorch CPU restatement on a bounded row sample (N = 1)
+
+``--impl reference`` times the reference algorithm's CPU implementation (the
+PyTorch restatement under oracle/, all host threads) on a bounded row sample of
+the same workload and prints the same line with "impl": "reference".
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from trifast_b200.configs import WORKLOADS, make_inputs  # noqa: E402
+
+METRIC = "triangle_attention_fwd_bwd_tflops"
+
+
+def flops_fwd(w, rows=None):
+    rows = w.n if rows is None else rows
+    return 4.0 * w.batch * w.h * rows * w.n * w.n * w.d
+
+
+def flops_step(w, rows=None):
+    return flops_fwd(w, rows) * (3.5 if w.backward else 1.0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"burst": p["bf16_tflops"], "sustained": p["bf16_tflops_sustained"],
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# reference arm / CPU baseline: the PyTorch CPU restatement on a row sample
+# ---------------------------------------------------------------------------
+
+def cpu_sample_step(w, rows, seed=0):
+    """Returns a callable running fwd(+bwd) of `rows` pair rows on the CPU."""
+    from oracle import triangle_oracle as orc
+    q, k, v, b, m, do = make_inputs(w, seed=seed, sample_rows=rows)
+    # fp32 compute on fp32 copies of the rounded inputs: the reference's test oracle
+    # runs in fp32 (tests/unit/test_trifast.py:50 of the reference).
+    q, k, v, b, do = (t.float() for t in (q, k, v, b, do))
+
+    def step():
+        orc.forward_backward_chunked(q, k, v, b, m, do=do if w.backward else None,
+                                     rows_per_chunk=4)
+    return step
+
+
+def cpu_rows_for_budget(w, seconds):
+    """Rows whose fwd+bwd should take about `seconds` on this host (>= 4)."""
+    probe = 4
+    step = cpu_sample_step(w, probe)
+    step()
+    t0 = time.perf_counter()
+    step()
+    per_row = (time.perf_counter() - t0) / probe
+    return int(max(4, min(w.n, (seconds / max(per_row, 1e-6)) // 4 * 4)))
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    rows = cpu_rows_for_budget(w, 4.0)
+    step = cpu_sample_step(w, rows)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = flops_step(w, rows) / dt / 1e12
+    sample = f"{rows} of {w.n} pair rows per step, fp32 PyTorch CPU, time scaled by rows"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3 * w.n / rows, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample, "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(w, gpus):
+    return {"workload": w.name, "n": w.n, "heads": w.h, "head_dim": w.d, "batch": w.batch,
+            "mask": w.mask, "backward": w.backward,
+            "parallelism": f"row-shard x{gpus}" if gpus > 1 else "single GPU",
+            "l2": "inputs larger than L2 (no flush)"}
+
+
+# ---------------------------------------------------------------------------
+# native arm
+# ---------------------------------------------------------------------------
+
+class DirectStep:
+    """fwd (+bwd) through the C ABI with every buffer preallocated."""
+
+    def __init__(self, w, q, k, v, b, m, do, group_size):
+        from trifast_b200 import _lib
+        self.lib, self._lib = _lib.load(), _lib
+        self.w, self.world = w, group_size
+        bs, h, rows, n, d = q.shape
+        dev = q.device
+        self.t = dict(q=q, k=k, v=v, b=b, do=do)
+        self.m8 = m.view(torch.uint8)
+        self.o = torch.empty_like(q)
+        self.lse = torch.empty((bs, h, rows, n), dtype=torch.float32, device=dev)
+        self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype)
+        if w.backward:
+            self.dq, self.dk, self.dv = (torch.empty_like(q) for _ in range(3))
+            self.db = torch.empty_like(b)
+            self.db32 = torch.empty(b.shape, dtype=torch.float32, device=dev)
+            nbytes = self.lib.trifast_backward_workspace_bytes(C.byref(self.shape))
+            self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        L = _lib
+        self.a = {k_: L.t5(x) for k_, x in dict(q=q, k=k, v=v, do=do, o=self.o).items()}
+        self.ab, self.am = L.t4(b), L.mask_view(self.m8)
+        if w.backward:
+            self.a.update(dq=L.t5(self.dq), dk=L.t5(self.dk), dv=L.t5(self.dv))
+            self.adb = L.t4(self.db)
+        plan = L.pick_plan(bs, h, n, rows, d, q.dtype)
+        self.plan = plan
+        # launches per step: fwd 1; bwd: rowfull, delta, db, (split reduce), dq(+dkv), cast
+        self.launches = 1
+        if w.backward:
+            self.launches += 2 + 1 + (1 if plan["db_row_splits"] > 1 else 0) + 2 + 1
+
+    def forward(self):
+        a, B = self.a, C.byref
+        rc = self.lib.trifast_forward(B(self.shape), B(a["q"]), B(a["k"]), B(a["v"]), B(self.ab),
+                                      B(self.am), B(a["o"]), C.c_void_p(self.lse.data_ptr()),
+                                      self.stream)
+        self._lib.check(rc, "trifast_forward")
+
+    def backward_db(self):
+        a, B = self.a, C.byref
+        rc = self.lib.trifast_backward_db(
+            B(self.shape), B(a["do"]), B(a["q"]), B(a["k"]), B(a["v"]), B(self.ab), B(self.am),
+            B(a["o"]), C.c_void_p(self.lse.data_ptr()), C.c_void_p(self.db32.data_ptr()),
+            C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws.numel()), self.stream)
+        self._lib.check(rc, "trifast_backward_db")
+
+    def backward_dqkv(self):
+        a, B = self.a, C.byref
+        rc = self.lib.trifast_backward_dqkv(
+            B(self.shape), B(a["do"]), B(a["q"]), B(a["k"]), B(a["v"]), B(self.ab), B(self.am),
+            C.c_void_p(self.lse.data_ptr()), B(a["dq"]), B(a["dk"]), B(a["dv"]),
+            C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws.numel()), self.stream)
+        self._lib.check(rc, "trifast_backward_dqkv")
+
+    def finalize(self):
+        rc = self.lib.trifast_db_finalize(C.byref(self.shape), C.c_void_p(self.db32.data_ptr()),
+                                          C.byref(self.adb), self.stream)
+        self._lib.check(rc, "trifast_db_finalize")
+
+    def step(self):
+        import torch.distributed as dist
+        self.forward()
+        if not self.w.backward:
+            return
+        self.backward_db()
+        work = None
+        if self.world > 1:
+            work = dist.all_reduce(self.db32, async_op=True)
+        self.backward_dqkv()
+        if work is not None:
+            work.wait()
+        self.finalize()
+
+
+def time_events(fn, iters):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_native(args, w):
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from trifast_b200.dist import shard_rows, triangle_attention_row_sharded
+    rows = shard_rows(w.n, rank, world)
+    q, k, v, b, m, do = make_inputs(w, seed=0, rows=rows if world > 1 else None, device=dev)
+    torch.cuda.synchronize()
+    step = DirectStep(w, q, k, v, b, m, do, world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernels only, inputs resident -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step.step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = time_events(step.step, args.steps)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t)
+    rc = step.lib.trifast_check_device_status(step.stream)
+    step._lib.check(rc, "device status after the timed region")
+
+    # ---- end to end through the public API with host buffers ---------------------------
+    host = [t.cpu().pin_memory() for t in (q, k, v, b, m, do)]
+    outs_host = None
+
+    def e2e_step():
+        nonlocal outs_host
+        dq_, dk_, dv_, db_, dm_, ddo_ = (t.to(dev, non_blocking=True) for t in host)
+        for t in (dq_, dk_, dv_, db_):
+            t.requires_grad_(w.backward)
+        if world > 1:
+            o = triangle_attention_row_sharded(dq_, dk_, dv_, db_, dm_)
+        else:
+            from trifast_b200 import triangle_attention
+            o = triangle_attention(dq_, dk_, dv_, db_, dm_)
+        res = [o]
+        if w.backward:
+            o.backward(ddo_)
+            res += [dq_.grad, dk_.grad, dv_.grad, db_.grad]
+        if outs_host is None:
+            outs_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in res]
+        for dst, src in zip(outs_host, res):
+            dst.copy_(src.detach(), non_blocking=True)
+        return res
+
+    e2e_iters = max(2, min(args.steps, 5))
+    e2e_step()
+    e2e_step()
+    barrier()
+    e2e_ms = time_events(e2e_step, e2e_iters)
+    barrier()
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t)
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = sum(t.numel() * t.element_size() for t in outs_host)
+    del host, outs_host
+    total_flops = flops_step(w)
+
+    # ---- per-phase timing, roofline and the CPU baseline (single GPU only) ------------
+    phases, roofline, cpu = None, None, None
+    peaks = measured_peaks()
+    if world == 1:
+        phases = {"forward": time_events(step.forward, args.steps)}
+        kernels_flops = {"forward": flops_fwd(w)}
+        if w.backward:
+            phases["backward_db"] = time_events(step.backward_db, args.steps)
+            phases["backward_dqkv"] = time_events(step.backward_dqkv, args.steps)
+            # contractions each phase executes: db recomputes S and dP (2 of them);
+            # dq+dk+dv executes S, dP (twice when dq and dk/dv are separate kernels), dQ, dK, dV
+            kernels_flops["backward_db"] = flops_fwd(w)
+            kernels_flops["backward_dqkv"] = 2.5 * flops_fwd(w)
+        top = max(phases, key=phases.get)
+        ach = kernels_flops[top] / (phases[top] * 1e-3) / 1e12
+        peak = peaks["burst"]
+        roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak,
+                    "unit": "TFLOP/s", "frac": ach / peak,
+                    "peak_source": f"bf16 burst, {peaks['source']}", "traffic": None,
+                    "step_frac_of_peak": total_flops / (ms * 1e-3) / 1e12 / peak,
+                    "step_frac_of_sustained": total_flops / (ms * 1e-3) / 1e12 / peaks["sustained"]}
+        try:
+            prof = os.path.join(ROOT, "profiles", "traffic.json")
+            if os.path.exists(prof):
+                with open(prof) as f:
+                    roofline["traffic"] = json.load(f).get(w.name, {}).get(top)
+        except (OSError, ValueError):
+            pass
+        if rank == 0 and not args.no_cpu_baseline:
+            crow = cpu_rows_for_budget(w, 8.0)
+            cstep = cpu_sample_step(w, crow)
+            cstep()
+            t0 = time.perf_counter()
+            cstep()
+            dt = time.perf_counter() - t0
+            cpu = {"value": flops_step(w, crow) / dt / 1e12, "unit": "TFLOP/s",
+                   "cores": torch.get_num_threads(), "kind": "port", "host_cpus": os.cpu_count(),
+                   "sample": f"{crow} of {w.n} pair rows, fp32 PyTorch CPU restatement, "
+                             f"{dt:.1f} s; full step would be {dt * w.n / crow:.0f} s"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": total_flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": str(w.dtype).replace("torch.", ""),
+            "data": "synthetic", "config": workload_config(w, world),
+            "plan": step.plan, "clocks": clocks,
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": step.launches * args.steps,
+            "frac_of_bf16_peak": {"measured_burst": total_flops / (ms * 1e-3) / 1e12 / peaks["burst"],
+                                  "measured_sustained": total_flops / (ms * 1e-3) / 1e12 / peaks["sustained"],
+                                  "nominal_2250": total_flops / (ms * 1e-3) / 1e12 / 2250.0},
+        }
+        if phases is not None:
+            line["phases_ms"] = phases
+            line["roofline"] = roofline
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="metric_n1024", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_native(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,16 +65,19 @@ def make_mask(w: Workload, seed: int, device="cpu") -> torch.Tensor:
     raise ValueError(w.mask)
 
 
-def make_inputs(w: Workload, seed: int = 1337, rows: slice | None = None, device="cpu"):
+def make_inputs(w: Workload, seed: int = 1337, rows: slice | None = None, device="cpu",
+                sample_rows: int | None = None):
     """Tensors (q, k, v, bias, mask, dO) of workload ``w`` in its dtype.
 
     Drawn on ``device`` (parity tests draw on the CPU and copy, so checker and
     kernels see the same bits; the benchmark draws on the GPU).  ``rows``
     selects a pair-row shard of q, k, v, mask and dO after the draw, so every
-    shard of one seed comes from the same full-size tensors.
+    shard of one seed comes from the same full-size tensors.  ``sample_rows``
+    instead draws only that many pair rows directly (same distributions, not the
+    same values as the full draw): the bounded sample of the CPU timing legs.
     """
     g = torch.Generator(device=device).manual_seed(seed)
-    shape = (w.batch, w.h, w.n, w.n, w.d)
+    shape = (w.batch, w.h, sample_rows or w.n, w.n, w.d)
     s = w.d ** -0.5
 
     def draw(shp, std):
@@ -86,6 +89,8 @@ def make_inputs(w: Workload, seed: int = 1337, rows: slice | None = None, device
     bias = draw((w.batch, w.h, w.n, w.n), w.bias_std)
     do = draw(shape, 1.0)
     mask = make_mask(w, seed, device)
+    if sample_rows:
+        mask = mask[:, :sample_rows].contiguous()
     if rows is not None:
         q, k, v, do = (t[:, :, rows].contiguous() for t in (q, k, v, do))
         mask = mask[:, rows].contiguous()
