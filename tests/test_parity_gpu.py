@@ -21,6 +21,18 @@ from trifast_b200.utils import gen_tensors
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def device_status_is_clean():
+    """No kernel may have given up on one of its bounded waits during a test."""
+    yield
+    import ctypes
+    from trifast_b200 import _lib
+    rc = _lib.load().trifast_check_device_status(
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, _lib.status_str(rc)
+
 NAMES = ("o", "dq", "dk", "dv", "db")
 
 

@@ -1,6 +1,485 @@
-// placeholder until the tcgen05 forward lands
+// Forward triangle attention on the 5th-generation tensor cores (bf16 / fp16).
+//
+// One CTA owns a 128-query tile (h, j-tile) of R consecutive pair rows i ("slots")
+// and walks the keys in tiles of 128.  The R slots share every bias tile, which
+// is the dominant shared-memory stream (32 KiB per step against 8-16 KiB of K+V
+// per slot), and give the tensor pipe independent work while the softmax of the
+// other slot runs.
+//
+//   warps 0 .. 4R-1 : softmax warpgroups, one per slot; thread t owns query row t:
+//                     S (TMEM) -> registers, + bias (shared memory), mask, online
+//                     softmax in fp32, P -> TMEM as 16-bit pairs, O rescale when
+//                     the row maximum moves, final O / l and lse
+//   warp 4R         : TMA producer (one lane): Q once, then K, V (per slot) and
+//                     the bias tile per key step through an NS-deep ring
+//   warp 4R + 1     : MMA issuer (one lane): S = Q K^T (SS, both operands K-major)
+//                     and O += P V (A = P from TMEM, B = V as an MN-major tile)
+//
+// TMEM columns per slot r (base r * 256): S [0,128) fp32, P [128,192) packed
+// 16-bit pairs, O [192, 192 + D) fp32.
+//
+// Semantics follow the PyTorch path of the reference (src/trifast/equiv.py:42-69):
+// masked keys weigh exactly zero; rows whose keys are all masked get uniform
+// weights over all n keys and lse = finfo(dtype).min.  The kernel stands in for
+// `_fwd` of the reference (src/trifast/triton.py:14-132); unlike it, the scale
+// d^-0.5 is applied to the fp32 accumulator, not to Q in 16 bits.
+
+#include <math.h>
+
+#include <mutex>
+
 #include "kernels.h"
+#include "tc_common.cuh"
+
 namespace trifast {
-bool tc_forward_supported(const Dims&, int, const FwdArgs*) { return false; }
-cudaError_t tc_forward(const FwdArgs&, const trifast_plan&, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+using namespace tc;
+
+constexpr int kBJ = 128, kBK = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kMaxInit = -1e30f;
+constexpr int kSmemLimit = 232448;  // 227 KiB opt-in limit per CTA
+constexpr int kHeaderBytes = 512;
+
+template <int D, int R, int NS>
+struct FwdCfg {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kTileBytes = 128 * kRowBytes;      // one Q / K / V tile
+  static constexpr int kBiasBytes = 128 * 128 * 2;        // two [128 x 64] boxes
+  static constexpr int kStageBytes = 2 * R * kTileBytes + kBiasBytes;
+  static constexpr int kTilesBytes = R * kTileBytes + NS * kStageBytes;
+  static constexpr int kThreads = R * 128 + 64;
+  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
+  static int smem_bytes(int n) {
+    const int nkt = (n + kBK - 1) / kBK;
+    const int head = (kHeaderBytes + R * nkt * 16 + 1023) / 1024 * 1024;
+    return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
+  }
+};
+
+enum BarIdx { kQFull = 0, kFull = 1 };
+
+template <typename T, int D, int R, int NS>
+__global__ void __launch_bounds__(R * 128 + 64, 1)
+tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
+              View5 o, float* __restrict__ lse, MaskView mask, Dims dm, unsigned int* status) {
+  using Cfg = FwdCfg<D, R, NS>;
+  constexpr int EMPTY = kFull + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
+                P_READY = S_FREE + R, O_DONE = P_READY + R, NBARS = O_DONE + R;
+  static_assert(NBARS * 8 <= 256, "barrier area");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
+  int* open_flag = reinterpret_cast<int*>(gbase + 264);           // [R]
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [R][nkt][4]
+
+  const int n = dm.n;
+  const int nkt = (n + kBK - 1) / kBK;
+  const uint32_t tiles_off = (kHeaderBytes + R * nkt * 16 + 1023u) & ~1023u;
+  const uint32_t tiles = base + tiles_off;
+  auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
+  auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kTileBytes; };
+  auto stage_base = [&](int s) -> uint32_t {
+    return tiles + R * Cfg::kTileBytes + s * Cfg::kStageBytes;
+  };
+  auto k_tile = [&](int s, int r) -> uint32_t { return stage_base(s) + r * Cfg::kTileBytes; };
+  auto v_tile = [&](int s, int r) -> uint32_t {
+    return stage_base(s) + (R + r) * Cfg::kTileBytes;
+  };
+  auto bias_off = [&](int s) -> uint32_t {  // byte offset from gbase
+    return tiles_off + R * Cfg::kTileBytes + s * Cfg::kStageBytes + 2 * R * Cfg::kTileBytes;
+  };
+
+  // A wait that gave up in an earlier CTA or launch leaves the status word set:
+  // stop doing work until the host has read and cleared it.
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int jt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int nslots = min(R, dm.n_rows - i0);
+
+  if (tid == 0) {
+    mbar_init(bar(kQFull), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar(kFull + s), 1);
+      mbar_init(bar(EMPTY + s), nslots * 5);  // per slot: 1 MMA commit + 4 softmax warps
+    }
+    for (int r = 0; r < R; ++r) {
+      mbar_init(bar(S_FULL + r), 1);
+      mbar_init(bar(S_FREE + r), 4);
+      mbar_init(bar(P_READY + r), 4);
+      mbar_init(bar(O_DONE + r), 1);
+      open_flag[r] = 0;
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 * R + 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 * R && lane == 0) {
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4 * R) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar(kQFull), nslots * Cfg::kTileBytes);
+      for (int r = 0; r < nslots; ++r)
+        tma_load_5d(q_tile(r), &map_q, bar(kQFull), 0, jt * kBJ, i0 + r, h, b);
+      for (int kt = 0; kt < nkt; ++kt) {
+        const int s = kt % NS;
+        if (kt >= NS && !mbar_wait(bar(EMPTY + s), ((kt / NS) - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(bar(kFull + s), nslots * 2 * Cfg::kTileBytes + Cfg::kBiasBytes);
+        for (int r = 0; r < nslots; ++r) {
+          tma_load_5d(k_tile(s, r), &map_k, bar(kFull + s), 0, kt * kBK, i0 + r, h, b);
+          tma_load_5d(v_tile(s, r), &map_v, bar(kFull + s), 0, kt * kBK, i0 + r, h, b);
+        }
+        const uint32_t bias_s = base + bias_off(s);
+        tma_load_4d(bias_s, &map_b, bar(kFull + s), kt * kBK, jt * kBJ, h, b);
+        tma_load_4d(bias_s + 16384, &map_b, bar(kFull + s), kt * kBK + 64, jt * kBJ, h, b);
+      }
+    }
+  } else if (warp == 4 * R + 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+      constexpr uint32_t idesc_qk = make_idesc(128, 128, kBf16, false, false);
+      constexpr uint32_t idesc_pv = make_idesc(128, D, kBf16, false, true);
+      auto issue_qk = [&](int r, int s) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+          const uint64_t bd = make_smem_desc(k_tile(s, r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+          umma_ss(tmem_base + r * 256, ad, bd, idesc_qk, kk > 0);
+        }
+        umma_commit(bar(S_FULL + r));
+      };
+      bool ok = mbar_wait(bar(kQFull), 0, abort_flag) && mbar_wait(bar(kFull), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        for (int r = 0; r < nslots; ++r) issue_qk(r, 0);
+      }
+      for (int kt = 0; kt < nkt && ok; ++kt) {
+        const int s = kt % NS;
+        if (kt + 1 < nkt) {
+          const int ns = (kt + 1) % NS;
+          ok = mbar_wait(bar(kFull + ns), ((kt + 1) / NS) & 1, abort_flag);
+          for (int r = 0; r < nslots && ok; ++r) {
+            ok = mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(r, ns);
+          }
+        }
+        for (int r = 0; r < nslots && ok; ++r) {
+          ok = mbar_wait(bar(P_READY + r), kt & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kBK / 16; ++ks) {
+            const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                               Cfg::kSbo, Cfg::kSwz);
+            umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
+                    (kt > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(bar(O_DONE + r));
+          umma_commit(bar(EMPTY + s));
+        }
+      }
+    }
+  } else if (warp / 4 < nslots) {
+    // ------------------------------------------------------------ softmax warpgroup
+    const int r = warp / 4, wq = warp & 3, t = tid & 127;
+    const int i = i0 + r;
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + r * 256;
+    const uint32_t tP = tS + 128, tO = tS + 192;
+    uint32_t* mb = maskbits + r * nkt * 4;
+
+    {  // key mask of row i as bit words; bit set = key dropped (or beyond n)
+      const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+      int any_open = 0;
+      for (int kt = 0; kt < nkt; ++kt) {
+        const int key = kt * kBK + t;
+        const int dropped = (key < n) ? (mrow[key] != 0) : 1;
+        any_open |= (key < n) && !dropped;
+        const uint32_t bits = __ballot_sync(0xffffffffu, dropped);
+        if (lane == 0) mb[kt * 4 + wq] = bits;
+      }
+      if (__any_sync(0xffffffffu, any_open) && lane == 0) atomicOr(&open_flag[r], 1);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
+    }
+    const bool row_full = open_flag[r] == 0;
+
+    float m_run = kMaxInit, l_run = 0.f;
+    bool ok = true;
+    for (int kt = 0; kt < nkt; ++kt) {
+      const int s = kt % NS;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), kt & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      float x[128];
+      {
+        uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+        tmem_ld32(tS + 0, xr + 0);
+        tmem_ld32(tS + 32, xr + 32);
+        tmem_ld32(tS + 64, xr + 64);
+        tmem_ld32(tS + 96, xr + 96);
+        tmem_wait_ld();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_FREE + r));
+
+      // mask words of this key tile (uniform over the warpgroup)
+      uint32_t mw[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        if (row_full) {  // only keys beyond n stay dropped
+          const int valid = n - (kt * kBK + 32 * w);
+          mw[w] = valid >= 32 ? 0u : (valid <= 0 ? 0xffffffffu : ~((1u << valid) - 1u));
+        } else {
+          mw[w] = mb[kt * 4 + w];
+        }
+      }
+      const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(kFull + s), (kt / NS) & 1, abort_flag));
+      if (!ok) break;
+      if (row_full) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) x[c] = 0.f;
+      } else {
+        const uint8_t* brow = gbase + bias_off(s) + t * 128;
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          const uint4 u = *reinterpret_cast<const uint4*>(brow + (g >> 3) * 16384 +
+                                                          (((g & 7) ^ (t & 7)) << 4));
+          float b0, b1;
+          unpack2<T>(u.x, b0, b1);
+          x[g * 8 + 0] = fmaf(x[g * 8 + 0], dm.scale, b0);
+          x[g * 8 + 1] = fmaf(x[g * 8 + 1], dm.scale, b1);
+          unpack2<T>(u.y, b0, b1);
+          x[g * 8 + 2] = fmaf(x[g * 8 + 2], dm.scale, b0);
+          x[g * 8 + 3] = fmaf(x[g * 8 + 3], dm.scale, b1);
+          unpack2<T>(u.z, b0, b1);
+          x[g * 8 + 4] = fmaf(x[g * 8 + 4], dm.scale, b0);
+          x[g * 8 + 5] = fmaf(x[g * 8 + 5], dm.scale, b1);
+          unpack2<T>(u.w, b0, b1);
+          x[g * 8 + 6] = fmaf(x[g * 8 + 6], dm.scale, b0);
+          x[g * 8 + 7] = fmaf(x[g * 8 + 7], dm.scale, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+
+      if (!clean) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if ((mw[c >> 5] >> (c & 31)) & 1u) x[c] = -INFINITY;
+      }
+      float mt = x[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mt = fmaxf(mt, x[c]);
+      const float m_new = fmaxf(m_run, mt);
+      const float neg = -m_new * kLog2e;
+      const float alpha = ex2(fmaf(m_run, kLog2e, neg));
+      float sum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        const float p0 = ex2(fmaf(x[c], kLog2e, neg));
+        const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
+        sum += p0 + p1;
+        pk[c >> 1] = pack2<T>(p0, p1);
+      }
+      l_run = fmaf(l_run, alpha, sum);
+      m_run = m_new;
+
+      if (kt > 0) {
+        // PV of the previous key tile must be done before O is rescaled and P reused.
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (kt - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t acc[32];
+            tmem_ld32(tO + 32 * c, acc);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+            tmem_st32(tO + 32 * c, acc);
+          }
+        }
+      }
+      tmem_st32(tP + 0, pk + 0);
+      tmem_st32(tP + 32, pk + 32);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_READY + r));
+    }
+
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (nkt - 1) & 1, abort_flag));
+    if (ok) {
+      tc_fence_after();
+      const int j = jt * kBJ + t;
+      const float inv = 1.f / l_run;
+      T* dst = reinterpret_cast<T*>(o.p) + b * o.sb + h * o.sh + (int64_t)i * o.si + (int64_t)j * o.sj;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(tO + 32 * c, acc);
+        tmem_wait_ld();
+        if (j < n) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 u;
+            u.x = pack2<T>(__uint_as_float(acc[e + 0]) * inv, __uint_as_float(acc[e + 1]) * inv);
+            u.y = pack2<T>(__uint_as_float(acc[e + 2]) * inv, __uint_as_float(acc[e + 3]) * inv);
+            u.z = pack2<T>(__uint_as_float(acc[e + 4]) * inv, __uint_as_float(acc[e + 5]) * inv);
+            u.w = pack2<T>(__uint_as_float(acc[e + 6]) * inv, __uint_as_float(acc[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 32 * c + e) = u;
+          }
+        }
+      }
+      if (j < n)
+        lse[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + j] =
+            row_full ? dm.sentinel : fmaf(lg2(l_run), kLn2, m_run);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up: let copies and MMAs in flight land before TMEM and shared
+    // memory are released, then report through the status word.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+    if (tid == 0) atomicOr(status, (unsigned int)kStatusTimeoutFwd);
+    __syncthreads();
+  }
+  if (warp == 4 * R + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
 }
+
+template <typename T, int D, int R, int NS>
+cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
+  using Cfg = FwdCfg<D, R, NS>;
+  const Dims& dm = a.dm;
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  const uint64_t eb = 2;
+  CUtensorMap mq, mk, mv, mbias;
+  const uint64_t dims5[5] = {(uint64_t)D, (uint64_t)dm.n, (uint64_t)dm.n_rows, (uint64_t)dm.heads,
+                             (uint64_t)dm.batch};
+  const uint32_t box5[5] = {(uint32_t)D, 128, 1, 1, 1};
+  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  auto map5 = [&](CUtensorMap* m, const View5& v) {
+    const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
+                            (uint64_t)v.sb * eb};
+    return make_tensor_map(m, bf16, 5, v.p, dims5, st, box5, swz);
+  };
+  if (!map5(&mq, a.q) || !map5(&mk, a.k) || !map5(&mv, a.v)) return cudaErrorInvalidValue;
+  {
+    const uint64_t dims4[4] = {(uint64_t)dm.n, (uint64_t)dm.n, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    const uint32_t box4[4] = {64, 128, 1, 1};
+    if (!make_tensor_map(&mbias, bf16, 4, a.bias.p, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+  }
+  const int smem = Cfg::smem_bytes(dm.n);
+  auto kern = tc_fwd_kernel<T, D, R, NS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((dm.n + kBJ - 1) / kBJ, (dm.n_rows + R - 1) / R, dm.batch * dm.heads);
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, dm, a.status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+namespace tc {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+bool make_tensor_map(CUtensorMap* map, bool bf16, int rank, void* base, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return false;
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) {
+    uint64_t s = strides_bytes[i];
+    // extent-1 dimensions may come with arbitrary strides: give them the dense pitch
+    if (dims[i + 1] == 1) s = (i == 0) ? dims[0] * 2 : gstr[i - 1] * dims[i];
+    if (s == 0 || (s & 15)) return false;
+    gstr[i] = s;
+  }
+  const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
+bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
+  if (dtype != TRIFAST_BF16 && dtype != TRIFAST_F16) return false;
+  if (dm.d != 32 && dm.d != 64) return false;
+  if (dm.n % 8 != 0 || dm.n < 128) return false;
+  const int smem = (dm.d == 32) ? FwdCfg<32, 2, 3>::smem_bytes(dm.n) : FwdCfg<64, 2, 2>::smem_bytes(dm.n);
+  if (smem > kSmemLimit) return false;
+  if (a) {
+    if ((a->bias.sj * 2) % 16 || (a->bias.sh * 2) % 16 || (a->bias.sb * 2) % 16) return false;
+    if (((uintptr_t)a->bias.p) & 15) return false;
+    if (((uintptr_t)a->o.p) & 15 || (a->o.sj * 2) % 16) return false;
+  }
+  return tc::get_encode_tiled() != nullptr;
+}
+
+cudaError_t tc_forward(const FwdArgs& a, const trifast_plan&, cudaStream_t s) {
+  const bool bf16 = a.dtype == TRIFAST_BF16;
+  if (a.dm.d == 32)
+    return bf16 ? launch<__nv_bfloat16, 32, 2, 3>(a, s) : launch<__half, 32, 2, 3>(a, s);
+  return bf16 ? launch<__nv_bfloat16, 64, 2, 2>(a, s) : launch<__half, 64, 2, 2>(a, s);
+}
+
+}  // namespace trifast
