@@ -185,6 +185,35 @@ int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
  * kernels have no such waits.) */
 int trifast_check_device_status(void* stream);
 
+/* The whole backward (same results as trifast_backward) for callers that cannot
+ * allocate device memory: a runtime that gave the whole GPU to its own pool at
+ * start-up, a plugin whose enqueue hook may not allocate, a latency-critical
+ * loop that cannot take cudaMalloc's implicit synchronisation.  The workspace
+ * is a fixed array inside the library instead of a caller buffer; the call
+ * allocates and frees nothing.  (No counterpart in the reference, whose host
+ * code always allocates through PyTorch.)
+ *
+ * Limit: trifast_backward_workspace_bytes(shape) must not exceed
+ * TRIFAST_STATIC_SCRATCH_BYTES (16 MiB, reserved on every GPU that loads the
+ * library until the process exits); larger problems return
+ * TRIFAST_ERR_TOO_LARGE and nothing is launched.  For bf16 at h = 4 that covers
+ * n up to 512.
+ *
+ * The first call on each device resolves the array's device address (that
+ * device must be current); make that first call outside any stream capture.
+ * All calls on a device share the one array, which keeps whatever the last
+ * call left in it: this call overwrites every region before reading it, so no
+ * clearing is needed, but two calls whose GPU work overlaps (different streams,
+ * or threads) race on it -- serialise them. */
+#define TRIFAST_STATIC_SCRATCH_BYTES ((size_t)16 << 20)
+int trifast_backward_static_scratch(const trifast_shape* shape,
+                                    const trifast_t5* d_o,
+                                    const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
+                                    const trifast_t4* bias, const trifast_mask* mask,
+                                    const trifast_t5* o, const float* lse,
+                                    const trifast_t5* dq, const trifast_t5* dk, const trifast_t5* dv,
+                                    const trifast_t4* db, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtrifast_b200.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+STATIC_SCRATCH_BYTES = 16 << 20   # TRIFAST_STATIC_SCRATCH_BYTES of the header
 _KERNEL_ENV = {"": 0, "auto": 0, "simt": 1, "tcgen05": 2}
 
 
@@ -62,6 +63,9 @@ SIGNATURES = {
                                         C.c_void_p, C.c_size_t, C.c_void_p]),
     "trifast_db_finalize": (C.c_int, [_P(Shape), C.c_void_p, _P(T4), C.c_void_p]),
     "trifast_check_device_status": (C.c_int, [C.c_void_p]),
+    "trifast_backward_static_scratch": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4),
+                                                  _P(Mask), _P(T5), C.c_void_p, _P(T5), _P(T5),
+                                                  _P(T5), _P(T4), C.c_void_p]),
 }
 
 _lib = None
