@@ -106,7 +106,8 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Carve-up of the backward workspace.
 struct Workspace {
-  size_t delta_off, rowfull_off, db_off, partial_off, total;
+  size_t delta_off, nlse_off, rowfull_off, db_off, bias_t_off, partial_off, total;
+  bool has_bias_t;
 };
 
 Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
@@ -116,10 +117,16 @@ Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   size_t off = 0;
   w.delta_off = off;
   off = align_up(off + stat, 256);
+  w.nlse_off = off;
+  off = align_up(off + stat, 256);
   w.rowfull_off = off;
   off = align_up(off + (size_t)s->batch * s->n_rows, 256);
   w.db_off = off;
   off = align_up(off + dbb, 256);
+  // transposed bias copy for the tensor-core dk/dv kernel (16-bit dtypes only)
+  w.has_bias_t = plan.kernel == TRIFAST_KERNEL_TCGEN05;
+  w.bias_t_off = off;
+  if (w.has_bias_t) off = align_up(off + dbb / 2, 256);
   w.partial_off = off;
   if (plan.db_row_splits > 1) off = align_up(off + dbb * plan.db_row_splits, 256);
   w.total = off;
@@ -201,6 +208,8 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->lse = lse;
   char* base = (char*)workspace;
   a->delta = (float*)(base + w.delta_off);
+  a->neg_lse2 = (float*)(base + w.nlse_off);
+  a->bias_t = w.has_bias_t ? (void*)(base + w.bias_t_off) : nullptr;
   a->rowfull = (uint8_t*)(base + w.rowfull_off);
   a->db_f32 = (float*)(base + w.db_off);
   a->db_partials = (float*)(base + w.partial_off);
@@ -320,7 +329,14 @@ int trifast_backward_dqkv(const trifast_shape* shape, const trifast_t5* d_o, con
   a.dq = make_view(dq);
   a.dk = make_view(dk);
   a.dv = make_view(dv);
-  return cuda_rc(simt_bwd_dqkv(a, (cudaStream_t)stream));
+  cudaStream_t s = (cudaStream_t)stream;
+  bool tc = c.plan.kernel == TRIFAST_KERNEL_TCGEN05;
+  if (tc && !tc_backward_supported(a)) {
+    if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
+    tc = false;
+  }
+  if ((rc = cuda_rc(tc ? tc_bwd_dq(a, s) : simt_bwd_dq(a, s)))) return rc;
+  return cuda_rc(tc ? tc_bwd_dkv(a, s) : simt_bwd_dkv(a, s));
 }
 
 int trifast_db_finalize(const trifast_shape* shape, const float* db_f32, const trifast_t4* db,

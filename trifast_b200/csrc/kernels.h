@@ -21,6 +21,8 @@ struct BwdArgs {
   MaskView mask;
   const float* lse;
   float* delta;          // (b, h, n_rows, n) fp32, in the workspace
+  float* neg_lse2;       // (b, h, n_rows, n) fp32: -lse * log2(e), in the workspace
+  void* bias_t;          // (b, h, k, j) transposed bias copy in the input dtype, or null
   uint8_t* rowfull;      // (b, n_rows): 1 = every key of the row is masked
   float* db_f32;         // (b, h, n, n) fp32 result of the row reduction
   float* db_partials;    // (splits, b, h, n, n) fp32, used when splits > 1
@@ -34,7 +36,8 @@ struct BwdArgs {
 cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s);
 cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s);   // delta + rowfull (all paths)
 cudaError_t simt_bwd_db(const BwdArgs& a, cudaStream_t s);
-cudaError_t simt_bwd_dqkv(const BwdArgs& a, cudaStream_t s);
+cudaError_t simt_bwd_dq(const BwdArgs& a, cudaStream_t s);
+cudaError_t simt_bwd_dkv(const BwdArgs& a, cudaStream_t s);
 cudaError_t db_reduce_splits(const BwdArgs& a, cudaStream_t s);
 cudaError_t db_cast(const float* db_f32, View4 db, int dtype, int batch, int heads, int n,
                     cudaStream_t s);
@@ -42,5 +45,8 @@ cudaError_t db_cast(const float* db_f32, View4 db, int dtype, int batch, int hea
 // tcgen05 kernels (tc_*.cu): bf16 / fp16.
 bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a);
 cudaError_t tc_forward(const FwdArgs& a, const trifast_plan& plan, cudaStream_t s);
+bool tc_backward_supported(const BwdArgs& a);
+cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s);
+cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s);
 
 }  // namespace trifast

@@ -94,7 +94,8 @@ __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowful
 // delta[b, h, i, j] = sum_d o * dO   (fp32; never rounded to the input dtype)
 // ---------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void delta_kernel(View5 o, View5 d_o, float* delta, Dims dm) {
+__global__ void delta_kernel(View5 o, View5 d_o, const float* lse, float* delta, float* neg_lse2,
+                             Dims dm) {
   const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -109,6 +110,26 @@ __global__ void delta_kernel(View5 o, View5 d_o, float* delta, Dims dm) {
 #pragma unroll
   for (int c = 0; c < D; ++c) acc = fmaf(to_f32<T>(po[c]), to_f32<T>(pd[c]), acc);
   delta[idx] = acc;
+  neg_lse2[idx] = -lse[idx] * 1.4426950408889634f;
+}
+
+// bias_t[b, h, k, j] = bias[b, h, j, k] for 2-byte elements (the dk/dv kernel reads
+// the bias with keys on the rows).
+__global__ void bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int n) {
+  __shared__ uint16_t tile[32][33];
+  const int bh = blockIdx.z, b = bh / heads, h = bh % heads;
+  const uint16_t* src = (const uint16_t*)bias.p + b * bias.sb + h * bias.sh;
+  uint16_t* dst = out + (int64_t)bh * n * n;
+  const int j0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int j = j0 + r, k = k0 + threadIdx.x;
+    if (j < n && k < n) tile[r][threadIdx.x] = src[(int64_t)j * bias.sj + k];
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int k = k0 + r, j = j0 + threadIdx.x;
+    if (j < n && k < n) dst[(int64_t)k * n + j] = tile[threadIdx.x][r];
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -494,11 +515,16 @@ cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s) {
 cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
   rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull);
+  if (a.bias_t) {
+    dim3 grid((dm.n + 31) / 32, (dm.n + 31) / 32, dm.batch * dm.heads);
+    bias_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n);
+  }
   return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
     using T = std::remove_pointer_t<decltype(tp)>;
     constexpr int D = decltype(dc)::value;
     const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
-    delta_kernel<T, D><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(a.o, a.d_o, a.delta, dm);
+    delta_kernel<T, D><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(a.o, a.d_o, a.lse, a.delta,
+                                                                     a.neg_lse2, dm);
   });
 }
 
@@ -523,7 +549,7 @@ cudaError_t db_reduce_splits(const BwdArgs& a, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-cudaError_t simt_bwd_dqkv(const BwdArgs& a, cudaStream_t s) {
+cudaError_t simt_bwd_dq(const BwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
   return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
     using T = std::remove_pointer_t<decltype(tp)>;
@@ -532,6 +558,14 @@ cudaError_t simt_bwd_dqkv(const BwdArgs& a, cudaStream_t s) {
     dim3 gq((dm.n + BJ - 1) / BJ, dm.n_rows, dm.batch * dm.heads);
     simt_dq_kernel<T, D, BJ, BK><<<gq, BJ, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.dq,
                                                    a.lse, a.delta, a.rowfull, dm);
+  });
+}
+
+cudaError_t simt_bwd_dkv(const BwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    constexpr int D = decltype(dc)::value;
     constexpr int BKT = 64, BJT = (D <= 32) ? 32 : 16;
     dim3 gk((dm.n + BKT - 1) / BKT, dm.n_rows, dm.batch * dm.heads);
     simt_dkv_kernel<T, D, BKT, BJT><<<gk, BKT, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o,

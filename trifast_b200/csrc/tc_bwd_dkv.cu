@@ -1,0 +1,481 @@
+// dk and dv of triangle attention on the tensor cores (bf16 / fp16).
+//
+// One CTA owns a 128-key tile of R consecutive pair rows ("slots") and walks the
+// queries in tiles of 64.  Everything is computed transposed, keys on the TMEM
+// lanes, so that P^T and dS^T feed the second pair of MMAs straight from TMEM:
+//     S^T  = K Q^T            (SS MMA, 128 keys x 64 queries)
+//     dP^T = V dO^T           (SS MMA)
+//     P^T  = exp2(S^T * c + bias^T * log2e - lse_j * log2e),  dS^T = P^T * (dP^T - delta_j)
+//            (the vector -lse * log2e is made once by the prepare step)
+//     dV  += P^T dO           (A = P^T from TMEM, B = dO tile as MN-major)
+//     dK  += dS^T Q           (A = dS^T from TMEM, B = Q tile as MN-major)
+// and at the end dk = dK * d^-0.5.  A thread owns one key, so the key mask is a
+// per-thread flag; lse and delta are per-column vectors read from shared memory;
+// the bias is read from a transposed copy (k-major) made by the prepare step, so
+// that a thread reads its row contiguously.
+//
+// Warps: 0 .. 4R-1 elementwise warpgroups, 4R TMA producer, 4R+1 MMA issuer,
+// 4R+2, 4R+3 idle.  TMEM columns per slot r (base r * 256): S^T [0,64),
+// dP^T [64,128), P^T [128,160), dS^T [160,192), dK [192, 192+D), dV [192+D, 192+2D)
+// (d = 64 runs one slot per CTA).
+//
+// Stands in for `_bwd_kv` of the reference (src/trifast/triton.py:137-263).
+
+#include <math.h>
+
+#include <type_traits>
+
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace trifast {
+namespace {
+using namespace tc;
+
+constexpr int kBKeys = 128, kBJ = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kSmemLimit = 232448;
+constexpr int kRegsIssue = 56, kRegsMath = 224;
+
+template <int D, int R, int NS>
+struct DkvCfg {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kKVBytes = 128 * kRowBytes;       // resident K or V tile
+  static constexpr int kQBytes = kBJ * kRowBytes;        // streamed Q or dO tile
+  static constexpr int kBiasBytes = 128 * kBJ * 2;       // bias^T tile: 128 keys x 64 queries
+  static constexpr int kVecBytes = kBJ * 4;              // lse or delta of 64 queries
+  static constexpr int kStageData = 2 * R * kQBytes + kBiasBytes + 2 * R * kVecBytes;
+  static constexpr int kStageBytes = (kStageData + 1023) / 1024 * 1024;
+  static constexpr int kTilesBytes = 2 * R * kKVBytes + NS * kStageBytes;
+  static constexpr int kThreads = R * 128 + 128;
+  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr int kSbo = 8 * kRowBytes;
+  static constexpr int kSlotCols = (R == 1) ? 512 : 256;
+  static int smem_bytes() { return 1024 + 1024 + kTilesBytes; }
+};
+
+template <typename T, int D, int R, int NS>
+__global__ void __launch_bounds__(R * 128 + 128, 1)
+tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+              const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+              const __grid_constant__ CUtensorMap map_bt, const __grid_constant__ CUtensorMap map_lse,
+              const __grid_constant__ CUtensorMap map_delta, View5 dk, View5 dv,
+              const uint8_t* __restrict__ rowfull, MaskView mask, Dims dm, unsigned int* status) {
+  using Cfg = DkvCfg<D, R, NS>;
+  constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
+                P_READY = S_FREE + R, ACC_DONE = P_READY + R, TOKEN = ACC_DONE + R,
+                NBARS = TOKEN + R;
+  static_assert(NBARS * 8 <= 256, "barrier area");
+  constexpr int kSlot = Cfg::kSlotCols;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
+
+  const int n = dm.n;
+  const int njt = (n + kBJ - 1) / kBJ;
+  constexpr uint32_t tiles_off = 1024;
+  auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
+  auto k_tile = [&](int r) -> uint32_t { return base + tiles_off + r * Cfg::kKVBytes; };
+  auto v_tile = [&](int r) -> uint32_t { return base + tiles_off + (R + r) * Cfg::kKVBytes; };
+  auto stage_off = [&](int s) -> uint32_t {
+    return tiles_off + 2 * R * Cfg::kKVBytes + s * Cfg::kStageBytes;
+  };
+  auto q_tile = [&](int s, int r) -> uint32_t { return base + stage_off(s) + r * Cfg::kQBytes; };
+  auto do_tile = [&](int s, int r) -> uint32_t {
+    return base + stage_off(s) + (R + r) * Cfg::kQBytes;
+  };
+  auto bias_off = [&](int s) -> uint32_t { return stage_off(s) + 2 * R * Cfg::kQBytes; };
+  auto lse_off = [&](int s, int r) -> uint32_t {
+    return bias_off(s) + Cfg::kBiasBytes + r * Cfg::kVecBytes;
+  };
+  auto delta_off = [&](int s, int r) -> uint32_t {
+    return bias_off(s) + Cfg::kBiasBytes + (R + r) * Cfg::kVecBytes;
+  };
+
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int nslots = min(R, dm.n_rows - i0);
+
+  if (tid == 0) {
+    mbar_init(bar(kInFull), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar(FULL + s), 1);
+      mbar_init(bar(EMPTY + s), nslots * 5);
+    }
+    for (int r = 0; r < R; ++r) {
+      mbar_init(bar(S_FULL + r), 1);
+      mbar_init(bar(S_FREE + r), 4);
+      mbar_init(bar(P_READY + r), 4);
+      mbar_init(bar(ACC_DONE + r), 1);
+      mbar_init(bar(TOKEN + r), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 * R + 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 * R && lane == 0) {
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_bt);
+    tma_prefetch_desc(&map_lse);
+    tma_prefetch_desc(&map_delta);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp >= 4 * R) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
+    if (warp == 4 * R) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar(kInFull), nslots * 2 * Cfg::kKVBytes);
+        for (int r = 0; r < nslots; ++r) {
+          tma_load_5d(k_tile(r), &map_k, bar(kInFull), 0, kt * kBKeys, i0 + r, h, b);
+          tma_load_5d(v_tile(r), &map_v, bar(kInFull), 0, kt * kBKeys, i0 + r, h, b);
+        }
+        for (int jt = 0; jt < njt; ++jt) {
+          const int s = jt % NS;
+          if (jt >= NS && !mbar_wait(bar(EMPTY + s), ((jt / NS) - 1) & 1, abort_flag)) break;
+          mbar_arrive_expect_tx(bar(FULL + s),
+                                nslots * (2 * Cfg::kQBytes + 2 * Cfg::kVecBytes) + Cfg::kBiasBytes);
+          for (int r = 0; r < nslots; ++r) {
+            tma_load_5d(q_tile(s, r), &map_q, bar(FULL + s), 0, jt * kBJ, i0 + r, h, b);
+            tma_load_5d(do_tile(s, r), &map_do, bar(FULL + s), 0, jt * kBJ, i0 + r, h, b);
+            tma_load_4d(base + lse_off(s, r), &map_lse, bar(FULL + s), jt * kBJ, i0 + r, h, b);
+            tma_load_4d(base + delta_off(s, r), &map_delta, bar(FULL + s), jt * kBJ, i0 + r, h, b);
+          }
+          tma_load_4d(base + bias_off(s), &map_bt, bar(FULL + s), jt * kBJ, kt * kBKeys, h, b);
+        }
+      }
+    } else if (warp == 4 * R + 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t idesc_s = make_idesc(128, kBJ, kBf16, false, false);
+        constexpr uint32_t idesc_acc = make_idesc(128, D, kBf16, false, true);
+        auto issue_s_dp = [&](int r, int s) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t ak = make_smem_desc(k_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            const uint64_t bq = make_smem_desc(q_tile(s, r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            umma_ss(tmem_base + r * kSlot, ak, bq, idesc_s, kk > 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t av = make_smem_desc(v_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            const uint64_t bg = make_smem_desc(do_tile(s, r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            umma_ss(tmem_base + r * kSlot + 64, av, bg, idesc_s, kk > 0);
+          }
+          umma_commit(bar(S_FULL + r));
+        };
+        bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          for (int r = 0; r < nslots; ++r) issue_s_dp(r, 0);
+        }
+        for (int jt = 0; jt < njt && ok; ++jt) {
+          const int s = jt % NS;
+          if (jt + 1 < njt) {
+            const int ns = (jt + 1) % NS;
+            ok = mbar_wait(bar(FULL + ns), ((jt + 1) / NS) & 1, abort_flag);
+            for (int r = 0; r < nslots && ok; ++r) {
+              ok = mbar_wait(bar(S_FREE + r), jt & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s_dp(r, ns);
+            }
+          }
+          for (int r = 0; r < nslots && ok; ++r) {
+            ok = mbar_wait(bar(P_READY + r), jt & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = (jt > 0) ? 1u : 0u;
+#pragma unroll
+            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO
+              const uint64_t bd = make_smem_desc(do_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * kSlot + 192 + D, tmem_base + r * kSlot + 128 + ks * 8, bd,
+                      idesc_acc, (ks > 0) ? 1u : acc);
+            }
+#pragma unroll
+            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dK += dS^T Q
+              const uint64_t bd = make_smem_desc(q_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * kSlot + 192, tmem_base + r * kSlot + 160 + ks * 8, bd,
+                      idesc_acc, (ks > 0) ? 1u : acc);
+            }
+            umma_commit(bar(ACC_DONE + r));
+            umma_commit(bar(EMPTY + s));
+          }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
+    if (warp / 4 < nslots) {
+      // ---------------------------------------------------------- elementwise warpgroup
+      const int r = warp / 4, wq = warp & 3, t = tid & 127;
+      const int i = i0 + r;
+      const int key = kt * kBKeys + t;
+      const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+      const uint32_t tS = tmem_base + lane_base + r * kSlot;
+      const uint32_t tDP = tS + 64, tP = tS + 128, tDS = tS + 160, tDK = tS + 192, tDV = tS + 192 + D;
+      const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+      // weight of this thread's key: 0 when dropped (or beyond n); on a fully masked
+      // row every key inside n weighs 1/n
+      const bool dropped =
+          key >= n || (!row_full && mask.p[b * mask.sb + (int64_t)i * mask.si + key] != 0);
+      const float c1 = dm.scale * kLog2e;
+      const float uniform = 1.f / (float)n;
+
+      bool ok = true;
+      // The key weight pattern is fixed for the whole query loop, so the loop is
+      // instantiated per pattern of this warp: 0 = every key kept (no selects),
+      // 1 = mixed, 2 = every key dropped (no exponentials), 3 = fully masked row.
+      const int mode = row_full ? 3
+                       : __all_sync(0xffffffffu, !dropped) ? 0
+                       : __all_sync(0xffffffffu, dropped)  ? 2
+                                                           : 1;
+      auto query_loop = [&](auto mode_tag) {
+      constexpr int kMode = decltype(mode_tag)::value;
+      for (int jt = 0; jt < njt; ++jt) {
+        const int s = jt % NS;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), jt & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        float x[64], g[64];
+        {
+          uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+          uint32_t* gr = reinterpret_cast<uint32_t*>(g);
+          tmem_ld32(tS + 0, xr + 0);
+          tmem_ld32(tS + 32, xr + 32);
+          tmem_ld32(tDP + 0, gr + 0);
+          tmem_ld32(tDP + 32, gr + 32);
+          tmem_wait_ld();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_FREE + r));
+
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (jt / NS) & 1, abort_flag));
+        if (!ok) break;
+        {
+          const uint8_t* brow = gbase + bias_off(s) + t * 128;
+          const float4* lse4 = reinterpret_cast<const float4*>(gbase + lse_off(s, r));
+          const float4* del4 = reinterpret_cast<const float4*>(gbase + delta_off(s, r));
+#pragma unroll
+          for (int q8 = 0; q8 < 8; ++q8) {
+            const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
+            const float4 la = lse4[q8 * 2], lb = lse4[q8 * 2 + 1];
+            const float4 da = del4[q8 * 2], db = del4[q8 * 2 + 1];
+            float b0, b1;
+            unpack2<T>(u.x, b0, b1);
+            x[q8 * 8 + 0] = fmaf(x[q8 * 8 + 0], c1, fmaf(b0, kLog2e, la.x));
+            x[q8 * 8 + 1] = fmaf(x[q8 * 8 + 1], c1, fmaf(b1, kLog2e, la.y));
+            unpack2<T>(u.y, b0, b1);
+            x[q8 * 8 + 2] = fmaf(x[q8 * 8 + 2], c1, fmaf(b0, kLog2e, la.z));
+            x[q8 * 8 + 3] = fmaf(x[q8 * 8 + 3], c1, fmaf(b1, kLog2e, la.w));
+            unpack2<T>(u.z, b0, b1);
+            x[q8 * 8 + 4] = fmaf(x[q8 * 8 + 4], c1, fmaf(b0, kLog2e, lb.x));
+            x[q8 * 8 + 5] = fmaf(x[q8 * 8 + 5], c1, fmaf(b1, kLog2e, lb.y));
+            unpack2<T>(u.w, b0, b1);
+            x[q8 * 8 + 6] = fmaf(x[q8 * 8 + 6], c1, fmaf(b0, kLog2e, lb.z));
+            x[q8 * 8 + 7] = fmaf(x[q8 * 8 + 7], c1, fmaf(b1, kLog2e, lb.w));
+            g[q8 * 8 + 0] -= da.x;
+            g[q8 * 8 + 1] -= da.y;
+            g[q8 * 8 + 2] -= da.z;
+            g[q8 * 8 + 3] -= da.w;
+            g[q8 * 8 + 4] -= db.x;
+            g[q8 * 8 + 5] -= db.y;
+            g[q8 * 8 + 6] -= db.z;
+            g[q8 * 8 + 7] -= db.w;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias^T, lse, delta consumed by this warp
+
+        if (jt > 0) {  // the accumulating MMAs of the previous query tile still read P^T, dS^T
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (jt - 1) & 1, abort_flag));
+          if (!ok) break;
+        }
+        if (R == 2 && nslots == 2) {  // the two slots alternate in the exp phase
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(bar(TOKEN + r), (r == 0) ? ((jt & 1) ^ 1) : (jt & 1), abort_flag));
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t pp[16], pd[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int c = ch * 32 + e;
+            float p0, p1;
+            if (kMode == 2) {
+              p0 = 0.f;
+              p1 = 0.f;
+            } else if (kMode == 3) {
+              p0 = uniform;
+              p1 = uniform;
+            } else {
+              p0 = ex2(x[c]);
+              p1 = ex2(x[c + 1]);
+            }
+            uint32_t wp = pack2<T>(p0, p1), wd = pack2<T>(p0 * g[c], p1 * g[c + 1]);
+            if (kMode == 1 || kMode == 3) {  // dropped keys weigh exactly zero
+              wp = dropped ? 0u : wp;
+              wd = dropped ? 0u : wd;
+            }
+            pp[e >> 1] = wp;
+            pd[e >> 1] = wd;
+          }
+          tmem_st16(tP + ch * 16, pp);
+          tmem_st16(tDS + ch * 16, pd);
+        }
+        if (R == 2 && nslots == 2) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + r));
+      }
+      };
+      switch (mode) {
+        case 0: query_loop(std::integral_constant<int, 0>{}); break;
+        case 1: query_loop(std::integral_constant<int, 1>{}); break;
+        case 2: query_loop(std::integral_constant<int, 2>{}); break;
+        default: query_loop(std::integral_constant<int, 3>{}); break;
+      }
+
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (njt - 1) & 1, abort_flag));
+      if (ok) {
+        tc_fence_after();
+        T* dst_k = reinterpret_cast<T*>(dk.p) + b * dk.sb + h * dk.sh + (int64_t)i * dk.si +
+                   (int64_t)key * dk.sj;
+        T* dst_v = reinterpret_cast<T*>(dv.p) + b * dv.sb + h * dv.sh + (int64_t)i * dv.si +
+                   (int64_t)key * dv.sj;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(tDK + 32 * c, acc);
+          tmem_wait_ld();
+          if (key < n) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 u;
+              u.x = pack2<T>(__uint_as_float(acc[e + 0]) * dm.scale, __uint_as_float(acc[e + 1]) * dm.scale);
+              u.y = pack2<T>(__uint_as_float(acc[e + 2]) * dm.scale, __uint_as_float(acc[e + 3]) * dm.scale);
+              u.z = pack2<T>(__uint_as_float(acc[e + 4]) * dm.scale, __uint_as_float(acc[e + 5]) * dm.scale);
+              u.w = pack2<T>(__uint_as_float(acc[e + 6]) * dm.scale, __uint_as_float(acc[e + 7]) * dm.scale);
+              *reinterpret_cast<uint4*>(dst_k + 32 * c + e) = u;
+            }
+          }
+          tmem_ld32(tDV + 32 * c, acc);
+          tmem_wait_ld();
+          if (key < n) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 u;
+              u.x = pack2<T>(__uint_as_float(acc[e + 0]), __uint_as_float(acc[e + 1]));
+              u.y = pack2<T>(__uint_as_float(acc[e + 2]), __uint_as_float(acc[e + 3]));
+              u.z = pack2<T>(__uint_as_float(acc[e + 4]), __uint_as_float(acc[e + 5]));
+              u.w = pack2<T>(__uint_as_float(acc[e + 6]), __uint_as_float(acc[e + 7]));
+              *reinterpret_cast<uint4*>(dst_v + 32 * c + e) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+    if (tid == 0) atomicOr(status, (unsigned int)kStatusTimeoutBwdDkv);
+    __syncthreads();
+  }
+  if (warp == 4 * R + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T, int D, int R, int NS>
+cudaError_t launch_dkv(const BwdArgs& a, cudaStream_t stream) {
+  using Cfg = DkvCfg<D, R, NS>;
+  const Dims& dm = a.dm;
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  const uint64_t eb = 2;
+  CUtensorMap mk, mv, mq, mdo, mbt, mlse, mdelta;
+  const uint64_t dims5[5] = {(uint64_t)D, (uint64_t)dm.n, (uint64_t)dm.n_rows, (uint64_t)dm.heads,
+                             (uint64_t)dm.batch};
+  const uint32_t box_kv[5] = {(uint32_t)D, 128, 1, 1, 1};
+  const uint32_t box_q[5] = {(uint32_t)D, (uint32_t)kBJ, 1, 1, 1};
+  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  auto map5 = [&](CUtensorMap* m, const View5& v, const uint32_t* box) {
+    const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
+                            (uint64_t)v.sb * eb};
+    return make_tensor_map(m, bf16, 5, v.p, dims5, st, box, swz);
+  };
+  if (!map5(&mk, a.k, box_kv) || !map5(&mv, a.v, box_kv) || !map5(&mq, a.q, box_q) ||
+      !map5(&mdo, a.d_o, box_q))
+    return cudaErrorInvalidValue;
+  {  // transposed bias copy: (b, h, k, j) contiguous
+    const uint64_t n = dm.n;
+    const uint64_t dims4[4] = {n, n, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st[3] = {n * eb, n * n * eb, n * n * dm.heads * eb};
+    const uint32_t box4[4] = {(uint32_t)kBJ, 128, 1, 1};
+    if (!make_tensor_map(&mbt, bf16, 4, a.bias_t, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+  }
+  {  // -lse * log2(e) and delta: (b, h, rows, n) fp32 contiguous, made by the prepare step
+    const uint64_t n = dm.n, rows = dm.n_rows;
+    const uint64_t dims4[4] = {n, rows, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st[3] = {n * 4, n * rows * 4, n * rows * dm.heads * 4};
+    const uint32_t box4[4] = {(uint32_t)kBJ, 1, 1, 1};
+    if (!make_tensor_map_f32(&mlse, 4, a.neg_lse2, dims4, st, box4) ||
+        !make_tensor_map_f32(&mdelta, 4, a.delta, dims4, st, box4))
+      return cudaErrorInvalidValue;
+  }
+  const int smem = Cfg::smem_bytes();
+  auto kern = tc_dkv_kernel<T, D, R, NS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((dm.n + kBKeys - 1) / kBKeys, (dm.n_rows + R - 1) / R, dm.batch * dm.heads);
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dk, a.dv,
+                                              a.rowfull, a.mask, dm, a.status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s) {
+  const bool bf16 = a.dtype == TRIFAST_BF16;
+  static_assert(DkvCfg<32, 2, 4>::kTilesBytes + 2048 <= kSmemLimit, "smem");
+  static_assert(DkvCfg<64, 1, 4>::kTilesBytes + 2048 <= kSmemLimit, "smem");
+  if (!a.bias_t || !a.neg_lse2) return cudaErrorInvalidValue;
+  if (a.dm.d == 32)
+    return bf16 ? launch_dkv<__nv_bfloat16, 32, 2, 4>(a, s) : launch_dkv<__half, 32, 2, 4>(a, s);
+  return bf16 ? launch_dkv<__nv_bfloat16, 64, 1, 4>(a, s) : launch_dkv<__half, 64, 1, 4>(a, s);
+}
+
+}  // namespace trifast

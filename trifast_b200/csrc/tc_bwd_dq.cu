@@ -1,0 +1,431 @@
+// dq of triangle attention on the tensor cores (bf16 / fp16).
+//
+// Same decomposition as the forward: one CTA owns a 128-query tile of two
+// consecutive pair rows ("slots", sharing the bias tiles) and walks the keys, in
+// tiles of 64.  Per slot and key tile:
+//     S  = Q K^T          (SS MMA, 128 x 64)      dP = dO V^T        (SS MMA, 128 x 64)
+//     P  = exp2(S * c + bias * log2e - lse * log2e)   (recomputed from the saved lse)
+//     dS = P * (dP - delta)  -> 16-bit -> TMEM
+//     dQ += dS K          (A = dS from TMEM, B = K as an MN-major tile)
+// and at the end dq = dQ * d^-0.5.
+//
+// Warps: 0-7 two elementwise warpgroups (thread = query row), 8 TMA producer,
+// 9 MMA issuer, 10-11 idle (they complete the warpgroup whose registers are
+// handed over with setmaxnreg).  TMEM columns per slot r (base r * 256):
+// S [0,64), dP [64,128), dS [128,160) as 16-bit pairs, dQ [160, 160 + D).
+//
+// Stands in for `_bwd_q` of the reference (src/trifast/triton.py:268-383); delta
+// comes from the fp32 workspace instead of being computed here and stored in the
+// input dtype.  Masked keys get exactly zero weight; rows whose keys are all
+// masked use P = 1/n (the PyTorch semantics, src/trifast/equiv.py:42-69).
+
+#include <math.h>
+
+#include <type_traits>
+
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace trifast {
+namespace {
+using namespace tc;
+
+constexpr int kBJ = 128, kBK = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kSmemLimit = 232448;
+constexpr int kHeaderBytes = 512;
+constexpr int kRegsIssue = 56, kRegsMath = 224;
+
+template <int D, int NS>
+struct DqCfg {
+  static constexpr int R = 2;
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kQBytes = 128 * kRowBytes;         // Q or dO tile
+  static constexpr int kKBytes = kBK * kRowBytes;         // K or V tile
+  static constexpr int kBiasBytes = 128 * kBK * 2;        // [128 x 64] box, 128-byte rows
+  static constexpr int kStageBytes = 2 * R * kKBytes + kBiasBytes;
+  static constexpr int kTilesBytes = 2 * R * kQBytes + NS * kStageBytes;
+  static constexpr int kThreads = R * 128 + 128;
+  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr int kSbo = 8 * kRowBytes;
+  static int mask_words(int n) { return ((n + 127) / 128) * 4; }
+  static int smem_bytes(int n) {
+    const int head = (kHeaderBytes + R * mask_words(n) * 4 + 1023) / 1024 * 1024;
+    return 1024 + head + kTilesBytes;
+  }
+};
+
+template <typename T, int D, int NS>
+__global__ void __launch_bounds__(384, 1)
+tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+             const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+             const __grid_constant__ CUtensorMap map_b, View5 dq, const float* __restrict__ lse,
+             const float* __restrict__ delta, const uint8_t* __restrict__ rowfull, MaskView mask,
+             Dims dm, unsigned int* status) {
+  using Cfg = DqCfg<D, NS>;
+  constexpr int R = Cfg::R;
+  constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
+                DS_READY = S_FREE + R, DQ_DONE = DS_READY + R, TOKEN = DQ_DONE + R,
+                NBARS = TOKEN + R;
+  static_assert(NBARS * 8 <= 256, "barrier area");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [R][mask_words]
+
+  const int n = dm.n;
+  const int nkt = (n + kBK - 1) / kBK;
+  const int mwords = ((n + 127) / 128) * 4;
+  const uint32_t tiles_off = (kHeaderBytes + R * mwords * 4 + 1023u) & ~1023u;
+  const uint32_t tiles = base + tiles_off;
+  auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
+  auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kQBytes; };
+  auto do_tile = [&](int r) -> uint32_t { return tiles + (R + r) * Cfg::kQBytes; };
+  auto stage_off = [&](int s) -> uint32_t {
+    return tiles_off + 2 * R * Cfg::kQBytes + s * Cfg::kStageBytes;
+  };
+  auto k_tile = [&](int s, int r) -> uint32_t { return base + stage_off(s) + r * Cfg::kKBytes; };
+  auto v_tile = [&](int s, int r) -> uint32_t {
+    return base + stage_off(s) + (R + r) * Cfg::kKBytes;
+  };
+  auto bias_off = [&](int s) -> uint32_t { return stage_off(s) + 2 * R * Cfg::kKBytes; };
+
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int jt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int nslots = min(R, dm.n_rows - i0);
+
+  if (tid == 0) {
+    mbar_init(bar(kInFull), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar(FULL + s), 1);
+      mbar_init(bar(EMPTY + s), nslots * 5);
+    }
+    for (int r = 0; r < R; ++r) {
+      mbar_init(bar(S_FULL + r), 1);
+      mbar_init(bar(S_FREE + r), 4);
+      mbar_init(bar(DS_READY + r), 4);
+      mbar_init(bar(DQ_DONE + r), 1);
+      mbar_init(bar(TOKEN + r), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 * R + 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 * R && lane == 0) {
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_do);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp >= 4 * R) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
+    if (warp == 4 * R) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar(kInFull), nslots * 2 * Cfg::kQBytes);
+        for (int r = 0; r < nslots; ++r) {
+          tma_load_5d(q_tile(r), &map_q, bar(kInFull), 0, jt * kBJ, i0 + r, h, b);
+          tma_load_5d(do_tile(r), &map_do, bar(kInFull), 0, jt * kBJ, i0 + r, h, b);
+        }
+        for (int kt = 0; kt < nkt; ++kt) {
+          const int s = kt % NS;
+          if (kt >= NS && !mbar_wait(bar(EMPTY + s), ((kt / NS) - 1) & 1, abort_flag)) break;
+          mbar_arrive_expect_tx(bar(FULL + s), nslots * 2 * Cfg::kKBytes + Cfg::kBiasBytes);
+          for (int r = 0; r < nslots; ++r) {
+            tma_load_5d(k_tile(s, r), &map_k, bar(FULL + s), 0, kt * kBK, i0 + r, h, b);
+            tma_load_5d(v_tile(s, r), &map_v, bar(FULL + s), 0, kt * kBK, i0 + r, h, b);
+          }
+          tma_load_4d(base + bias_off(s), &map_b, bar(FULL + s), kt * kBK, jt * kBJ, h, b);
+        }
+      }
+    } else if (warp == 4 * R + 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t idesc_s = make_idesc(128, kBK, kBf16, false, false);
+        constexpr uint32_t idesc_dq = make_idesc(128, D, kBf16, false, true);
+        auto issue_s_dp = [&](int r, int s) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t aq = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            const uint64_t bk = make_smem_desc(k_tile(s, r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            umma_ss(tmem_base + r * 256, aq, bk, idesc_s, kk > 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t ag = make_smem_desc(do_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            const uint64_t bv = make_smem_desc(v_tile(s, r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+            umma_ss(tmem_base + r * 256 + 64, ag, bv, idesc_s, kk > 0);
+          }
+          umma_commit(bar(S_FULL + r));
+        };
+        bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          for (int r = 0; r < nslots; ++r) issue_s_dp(r, 0);
+        }
+        for (int kt = 0; kt < nkt && ok; ++kt) {
+          const int s = kt % NS;
+          if (kt + 1 < nkt) {
+            const int ns = (kt + 1) % NS;
+            ok = mbar_wait(bar(FULL + ns), ((kt + 1) / NS) & 1, abort_flag);
+            for (int r = 0; r < nslots && ok; ++r) {
+              ok = mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s_dp(r, ns);
+            }
+          }
+          for (int r = 0; r < nslots && ok; ++r) {
+            ok = mbar_wait(bar(DS_READY + r), kt & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < kBK / 16; ++ks) {
+              const uint64_t bd = make_smem_desc(k_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * 256 + 160, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_dq,
+                      (kt > 0 || ks > 0) ? 1u : 0u);
+            }
+            umma_commit(bar(DQ_DONE + r));
+            umma_commit(bar(EMPTY + s));
+          }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
+    if (warp / 4 < nslots) {
+      // ---------------------------------------------------------- elementwise warpgroup
+      const int r = warp / 4, wq = warp & 3, t = tid & 127;
+      const int i = i0 + r;
+      const int j = jt * kBJ + t;
+      const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+      const uint32_t tS = tmem_base + lane_base + r * 256;
+      const uint32_t tDP = tS + 64, tDS = tS + 128, tDQ = tS + 160;
+      uint32_t* mb = maskbits + r * mwords;
+      const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+
+      {  // key mask of row i as bit words; bit set = key dropped (or beyond n)
+        const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+        for (int c = 0; c < mwords / 4; ++c) {
+          const int key = c * 128 + t;
+          const int dropped = (key < n) ? (row_full ? 0 : (mrow[key] != 0)) : 1;
+          const uint32_t bits = __ballot_sync(0xffffffffu, dropped);
+          if (lane == 0) mb[c * 4 + wq] = bits;
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
+      }
+      const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + min(j, n - 1);
+      const float neg_lse2 = -lse[stat] * kLog2e;
+      const float my_delta = delta[stat];
+      const float c1 = dm.scale * kLog2e;
+      const float uniform = 1.f / (float)n;
+
+      bool ok = true;
+      auto key_loop = [&](auto row_full_tag) {
+        constexpr bool kRowFull = decltype(row_full_tag)::value;
+        for (int kt = 0; kt < nkt; ++kt) {
+          const int s = kt % NS;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), kt & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          float x[64], g[64];
+          {
+            uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+            uint32_t* gr = reinterpret_cast<uint32_t*>(g);
+            tmem_ld32(tS + 0, xr + 0);
+            tmem_ld32(tS + 32, xr + 32);
+            tmem_ld32(tDP + 0, gr + 0);
+            tmem_ld32(tDP + 32, gr + 32);
+            tmem_wait_ld();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(S_FREE + r));
+
+          const uint32_t mw0 = mb[kt * 2 + 0], mw1 = mb[kt * 2 + 1];
+          const bool clean = (mw0 | mw1) == 0u;
+
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (kt / NS) & 1, abort_flag));
+          if (!ok) break;
+          if (!kRowFull) {
+            const uint8_t* brow = gbase + bias_off(s) + t * 128;
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+              const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
+              float b0, b1;
+              unpack2<T>(u.x, b0, b1);
+              x[q8 * 8 + 0] = fmaf(x[q8 * 8 + 0], c1, fmaf(b0, kLog2e, neg_lse2));
+              x[q8 * 8 + 1] = fmaf(x[q8 * 8 + 1], c1, fmaf(b1, kLog2e, neg_lse2));
+              unpack2<T>(u.y, b0, b1);
+              x[q8 * 8 + 2] = fmaf(x[q8 * 8 + 2], c1, fmaf(b0, kLog2e, neg_lse2));
+              x[q8 * 8 + 3] = fmaf(x[q8 * 8 + 3], c1, fmaf(b1, kLog2e, neg_lse2));
+              unpack2<T>(u.z, b0, b1);
+              x[q8 * 8 + 4] = fmaf(x[q8 * 8 + 4], c1, fmaf(b0, kLog2e, neg_lse2));
+              x[q8 * 8 + 5] = fmaf(x[q8 * 8 + 5], c1, fmaf(b1, kLog2e, neg_lse2));
+              unpack2<T>(u.w, b0, b1);
+              x[q8 * 8 + 6] = fmaf(x[q8 * 8 + 6], c1, fmaf(b0, kLog2e, neg_lse2));
+              x[q8 * 8 + 7] = fmaf(x[q8 * 8 + 7], c1, fmaf(b1, kLog2e, neg_lse2));
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+
+          if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (kt - 1) & 1, abort_flag));
+            if (!ok) break;
+          }
+          if (nslots == 2) {  // the two slots alternate in the exp phase (see the forward)
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait(bar(TOKEN + r), (r == 0) ? ((kt & 1) ^ 1) : (kt & 1), abort_flag));
+            if (!ok) break;
+          }
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 64; c += 2) {
+            float p0, p1;
+            if (kRowFull) {
+              p0 = uniform;
+              p1 = uniform;
+            } else {
+              p0 = ex2(x[c]);
+              p1 = ex2(x[c + 1]);
+            }
+            if (!clean) {
+              const uint32_t w = (c < 32) ? mw0 : mw1;
+              if ((w >> (c & 31)) & 1u) p0 = 0.f;
+              if ((w >> ((c + 1) & 31)) & 1u) p1 = 0.f;
+            }
+            pk[c >> 1] = pack2<T>(p0 * (g[c] - my_delta), p1 * (g[c + 1] - my_delta));
+          }
+          if (nslots == 2) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
+          }
+          tmem_st32(tDS, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(DS_READY + r));
+        }
+      };
+      if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
+
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (nkt - 1) & 1, abort_flag));
+      if (ok) {
+        tc_fence_after();
+        T* dst = reinterpret_cast<T*>(dq.p) + b * dq.sb + h * dq.sh + (int64_t)i * dq.si +
+                 (int64_t)j * dq.sj;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(tDQ + 32 * c, acc);
+          tmem_wait_ld();
+          if (j < n) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 u;
+              u.x = pack2<T>(__uint_as_float(acc[e + 0]) * dm.scale, __uint_as_float(acc[e + 1]) * dm.scale);
+              u.y = pack2<T>(__uint_as_float(acc[e + 2]) * dm.scale, __uint_as_float(acc[e + 3]) * dm.scale);
+              u.z = pack2<T>(__uint_as_float(acc[e + 4]) * dm.scale, __uint_as_float(acc[e + 5]) * dm.scale);
+              u.w = pack2<T>(__uint_as_float(acc[e + 6]) * dm.scale, __uint_as_float(acc[e + 7]) * dm.scale);
+              *reinterpret_cast<uint4*>(dst + 32 * c + e) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+    if (tid == 0) atomicOr(status, (unsigned int)kStatusTimeoutBwdDq);
+    __syncthreads();
+  }
+  if (warp == 4 * R + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T, int D, int NS>
+cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
+  using Cfg = DqCfg<D, NS>;
+  const Dims& dm = a.dm;
+  const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  const uint64_t eb = 2;
+  CUtensorMap mq, mdo, mk, mv, mbias;
+  const uint64_t dims5[5] = {(uint64_t)D, (uint64_t)dm.n, (uint64_t)dm.n_rows, (uint64_t)dm.heads,
+                             (uint64_t)dm.batch};
+  const uint32_t box_q[5] = {(uint32_t)D, 128, 1, 1, 1};
+  const uint32_t box_k[5] = {(uint32_t)D, (uint32_t)kBK, 1, 1, 1};
+  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  auto map5 = [&](CUtensorMap* m, const View5& v, const uint32_t* box) {
+    const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
+                            (uint64_t)v.sb * eb};
+    return make_tensor_map(m, bf16, 5, v.p, dims5, st, box, swz);
+  };
+  if (!map5(&mq, a.q, box_q) || !map5(&mdo, a.d_o, box_q) || !map5(&mk, a.k, box_k) ||
+      !map5(&mv, a.v, box_k))
+    return cudaErrorInvalidValue;
+  {
+    const uint64_t dims4[4] = {(uint64_t)dm.n, (uint64_t)dm.n, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    const uint32_t box4[4] = {(uint32_t)kBK, 128, 1, 1};
+    if (!make_tensor_map(&mbias, bf16, 4, a.bias.p, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+  }
+  const int smem = Cfg::smem_bytes(dm.n);
+  auto kern = tc_dq_kernel<T, D, NS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((dm.n + kBJ - 1) / kBJ, (dm.n_rows + 1) / 2, dm.batch * dm.heads);
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mbias, a.dq, a.lse, a.delta,
+                                              a.rowfull, a.mask, dm, a.status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_backward_supported(const BwdArgs& a) {
+  const Dims& dm = a.dm;
+  if (a.dtype != TRIFAST_BF16 && a.dtype != TRIFAST_F16) return false;
+  if (dm.d != 32 && dm.d != 64) return false;
+  if (dm.n % 8 != 0 || dm.n < 128) return false;
+  const int smem = (dm.d == 32) ? DqCfg<32, 4>::smem_bytes(dm.n) : DqCfg<64, 3>::smem_bytes(dm.n);
+  if (smem > kSmemLimit) return false;
+  if ((a.bias.sj * 2) % 16 || (a.bias.sh * 2) % 16 || (a.bias.sb * 2) % 16) return false;
+  if (((uintptr_t)a.bias.p) & 15) return false;
+  return tc::get_encode_tiled() != nullptr;
+}
+
+cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s) {
+  const bool bf16 = a.dtype == TRIFAST_BF16;
+  if (a.dm.d == 32)
+    return bf16 ? launch_dq<__nv_bfloat16, 32, 4>(a, s) : launch_dq<__half, 32, 4>(a, s);
+  return bf16 ? launch_dq<__nv_bfloat16, 64, 3>(a, s) : launch_dq<__half, 64, 3>(a, s);
+}
+
+}  // namespace trifast

@@ -141,6 +141,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+      "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+      "r"(r[15])
+      : "memory");
+}
+
 // ------------------------------------------------------------------ UMMA
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in bits [0,14),
 // leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46),
@@ -239,6 +249,9 @@ EncodeTiledFn get_encode_tiled();
 // rank <= 5; dims/box innermost first; strides_bytes[i] is the pitch of dim i+1.
 bool make_tensor_map(CUtensorMap* map, bool bf16, int rank, void* base, const uint64_t* dims,
                      const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz);
+// Same for an fp32 tensor, no swizzle (row vectors such as lse and delta).
+bool make_tensor_map_f32(CUtensorMap* map, int rank, void* base, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box);
 
 }  // namespace tc
 }  // namespace trifast

@@ -14,6 +14,8 @@
 //                     the bias tile per key step through an NS-deep ring
 //   warp 4R + 1     : MMA issuer (one lane): S = Q K^T (SS, both operands K-major)
 //                     and O += P V (A = P from TMEM, B = V as an MN-major tile)
+//   warps 4R+2, 4R+3: idle; they complete the warpgroup so that its registers can
+//                     be handed to the softmax warpgroups (setmaxnreg)
 //
 // TMEM columns per slot r (base r * 256): S [0,128) fp32, P [128,192) packed
 // 16-bit pairs, O [192, 192 + D) fp32.
@@ -35,6 +37,16 @@ namespace trifast {
 namespace {
 using namespace tc;
 
+// Registers per thread after the warpgroups rebalance (setmaxnreg): the last
+// warpgroup drops to kRegsIssue, the softmax warpgroups rise to kRegsSoftmax;
+// 2 * 128 * 224 + 128 * 56 = 64512 <= 65536.
+#ifndef TRIFAST_REG_DEC
+#define TRIFAST_REG_DEC 56
+#endif
+#ifndef TRIFAST_REG_INC
+#define TRIFAST_REG_INC 224
+#endif
+
 constexpr int kBJ = 128, kBK = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -49,7 +61,7 @@ struct FwdCfg {
   static constexpr int kBiasBytes = 128 * 128 * 2;        // two [128 x 64] boxes
   static constexpr int kStageBytes = 2 * R * kTileBytes + kBiasBytes;
   static constexpr int kTilesBytes = R * kTileBytes + NS * kStageBytes;
-  static constexpr int kThreads = R * 128 + 64;
+  static constexpr int kThreads = R * 128 + 128;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
   static int smem_bytes(int n) {
@@ -62,13 +74,14 @@ struct FwdCfg {
 enum BarIdx { kQFull = 0, kFull = 1 };
 
 template <typename T, int D, int R, int NS>
-__global__ void __launch_bounds__(R * 128 + 64, 1)
+__global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
               View5 o, float* __restrict__ lse, MaskView mask, Dims dm, unsigned int* status) {
   using Cfg = FwdCfg<D, R, NS>;
   constexpr int EMPTY = kFull + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                P_READY = S_FREE + R, O_DONE = P_READY + R, NBARS = O_DONE + R;
+                P_READY = S_FREE + R, O_DONE = P_READY + R, TOKEN = O_DONE + R,
+                NBARS = TOKEN + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
 
   extern __shared__ uint8_t smem_raw[];
@@ -117,6 +130,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(P_READY + r), 4);
       mbar_init(bar(O_DONE + r), 1);
+      mbar_init(bar(TOKEN + r), 4);
       open_flag[r] = 0;
     }
     *abort_flag = 0;
@@ -137,6 +151,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register budget: the last warpgroup (producer, MMA issuer, two idle warps)
+  // hands most of its registers to the softmax warpgroups, which keep a whole
+  // 128-column score row per thread.
+  if (warp >= 4 * R) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TRIFAST_REG_DEC));
   if (warp == 4 * R) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -204,7 +223,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
       }
     }
-  } else if (warp / 4 < nslots) {
+  }
+  } else {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TRIFAST_REG_INC));
+  if (warp / 4 < nslots) {
     // ------------------------------------------------------------ softmax warpgroup
     const int r = warp / 4, wq = warp & 3, t = tid & 127;
     const int i = i0 + r;
@@ -230,6 +252,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     float m_run = kMaxInit, l_run = 0.f;
     bool ok = true;
+    // The key loop exists in two copies, chosen once per row: the fully-masked-row
+    // case (every score is 0) must not merge with the regular case inside the
+    // loop, or the 128 live scores get duplicated and spill.
+    auto key_loop = [&](auto row_full_tag) {
+    constexpr bool kRowFull = decltype(row_full_tag)::value;
     for (int kt = 0; kt < nkt; ++kt) {
       const int s = kt % NS;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), kt & 1, abort_flag));
@@ -252,7 +279,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       uint32_t mw[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        if (row_full) {  // only keys beyond n stay dropped
+        if (kRowFull) {  // only keys beyond n stay dropped
           const int valid = n - (kt * kBK + 32 * w);
           mw[w] = valid >= 32 ? 0u : (valid <= 0 ? 0xffffffffu : ~((1u << valid) - 1u));
         } else {
@@ -263,7 +290,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
       ok = __all_sync(0xffffffffu, mbar_wait(bar(kFull + s), (kt / NS) & 1, abort_flag));
       if (!ok) break;
-      if (row_full) {
+      if (kRowFull) {
 #pragma unroll
         for (int c = 0; c < 128; ++c) x[c] = 0.f;
       } else {
@@ -295,22 +322,20 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         for (int c = 0; c < 128; ++c)
           if ((mw[c >> 5] >> (c & 31)) & 1u) x[c] = -INFINITY;
       }
-      float mt = x[0];
+      // Four independent chains for the row maximum and the row sum: with two
+      // warps per scheduler a single dependent chain of 128 would be latency-bound.
+      float mx[4] = {x[0], x[1], x[2], x[3]};
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mt = fmaxf(mt, x[c]);
+      for (int c = 4; c < 128; c += 4) {
+        mx[0] = fmaxf(mx[0], x[c + 0]);
+        mx[1] = fmaxf(mx[1], x[c + 1]);
+        mx[2] = fmaxf(mx[2], x[c + 2]);
+        mx[3] = fmaxf(mx[3], x[c + 3]);
+      }
+      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const float m_new = fmaxf(m_run, mt);
       const float neg = -m_new * kLog2e;
       const float alpha = ex2(fmaf(m_run, kLog2e, neg));
-      float sum = 0.f;
-      uint32_t pk[64];
-#pragma unroll
-      for (int c = 0; c < 128; c += 2) {
-        const float p0 = ex2(fmaf(x[c], kLog2e, neg));
-        const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
-        sum += p0 + p1;
-        pk[c >> 1] = pack2<T>(p0, p1);
-      }
-      l_run = fmaf(l_run, alpha, sum);
       m_run = m_new;
 
       if (kt > 0) {
@@ -330,13 +355,49 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           }
         }
       }
-      tmem_st32(tP + 0, pk + 0);
-      tmem_st32(tP + 32, pk + 32);
+      // The two slots take turns in the exp phase (it saturates the MUFU pipe on
+      // its own), so that one slot's loads, bias FMAs and maximum overlap the
+      // other's exponentials instead of both phases running in lockstep.  Slot 0
+      // goes first; each slot passes the turn on after issuing its exponentials.
+      if (R == 2 && nslots == 2) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bar(TOKEN + r), (r == 0) ? ((kt & 1) ^ 1) : (kt & 1), abort_flag));
+        if (!ok) break;
+      }
+      // exp and P store in chunks of 32 keys, so a packed chunk leaves the
+      // registers as soon as it is made; four independent partial sums.
+      float sm[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const int c = ch * 32 + e;
+          const float p0 = ex2(fmaf(x[c + 0], kLog2e, neg));
+          const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
+          const float p2 = ex2(fmaf(x[c + 2], kLog2e, neg));
+          const float p3 = ex2(fmaf(x[c + 3], kLog2e, neg));
+          sm[0] += p0;
+          sm[1] += p1;
+          sm[2] += p2;
+          sm[3] += p3;
+          pk[(e >> 1) + 0] = pack2<T>(p0, p1);
+          pk[(e >> 1) + 1] = pack2<T>(p2, p3);
+        }
+        tmem_st16(tP + ch * 16, pk);
+      }
+      l_run = fmaf(l_run, alpha, (sm[0] + sm[1]) + (sm[2] + sm[3]));
+      if (R == 2 && nslots == 2) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_READY + r));
     }
+    };
+    if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (nkt - 1) & 1, abort_flag));
     if (ok) {
@@ -365,6 +426,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         lse[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + j] =
             row_full ? dm.sentinel : fmaf(lg2(l_run), kLn2, m_run);
     }
+  }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -435,8 +497,9 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-bool make_tensor_map(CUtensorMap* map, bool bf16, int rank, void* base, const uint64_t* dims,
-                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+static bool encode(CUtensorMap* map, CUtensorMapDataType dt, uint64_t elem_bytes, int rank,
+                   void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                   const uint32_t* box, CUtensorMapSwizzle swz) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return false;
   cuuint64_t gdim[5], gstr[4];
@@ -449,14 +512,26 @@ bool make_tensor_map(CUtensorMap* map, bool bf16, int rank, void* base, const ui
   for (int i = 0; i + 1 < rank; ++i) {
     uint64_t s = strides_bytes[i];
     // extent-1 dimensions may come with arbitrary strides: give them the dense pitch
-    if (dims[i + 1] == 1) s = (i == 0) ? dims[0] * 2 : gstr[i - 1] * dims[i];
+    if (dims[i + 1] == 1) s = (i == 0) ? dims[0] * elem_bytes : gstr[i - 1] * dims[i];
     if (s == 0 || (s & 15)) return false;
     gstr[i] = s;
   }
-  const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                         (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = enc(map, dt, (cuuint32_t)rank, base, gdim, gstr, bx, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+bool make_tensor_map(CUtensorMap* map, bool bf16, int rank, void* base, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+  return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                rank, base, dims, strides_bytes, box, swz);
+}
+
+bool make_tensor_map_f32(CUtensorMap* map, int rank, void* base, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rank, base, dims, strides_bytes, box,
+                CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 }  // namespace tc
