@@ -106,7 +106,8 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Carve-up of the backward workspace.
 struct Workspace {
-  size_t delta_off, nlse_off, rowfull_off, db_off, bias_t_off, partial_off, total;
+  size_t delta_off, nlse_off, rowfull_off, maskbits_off, db_off, bias_t_off, partial_off, total;
+  int mask_words;
   bool has_bias_t;
 };
 
@@ -121,6 +122,9 @@ Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   off = align_up(off + stat, 256);
   w.rowfull_off = off;
   off = align_up(off + (size_t)s->batch * s->n_rows, 256);
+  w.mask_words = ((s->n + 127) / 128) * 4;
+  w.maskbits_off = off;
+  off = align_up(off + (size_t)s->batch * s->n_rows * w.mask_words * sizeof(uint32_t), 256);
   w.db_off = off;
   off = align_up(off + dbb, 256);
   // transposed bias copy for the tensor-core dk/dv kernel (16-bit dtypes only)
@@ -158,12 +162,16 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
     p->stages = 1;
   }
   // db: CTAs = tiles * splits.  Split the local rows until the grid covers the
-  // 148 SMs about twice, but never below 8 rows per split and at most 16 splits.
-  const int tile = 32;
+  // 148 SMs twice (CUDA-core kernel, 32 x 32 tiles, several CTAs per SM) or four
+  // times (tensor-core kernel, 128 x 128 tiles, one CTA per SM), but never below
+  // 8 rows per split and at most 16 splits.
+  const bool tc_db = kernel == TRIFAST_KERNEL_TCGEN05;
+  const int tile = tc_db ? 128 : 32;
+  const int64_t want = tc_db ? 592 : 296;
   const int64_t t = (s->n + tile - 1) / tile;
   const int64_t tiles = t * t * s->batch * s->heads;
   int splits = 1;
-  while (splits < 16 && tiles * splits < 296 && s->n_rows / (splits * 2) >= 8) splits *= 2;
+  while (splits < 16 && tiles * splits < want && s->n_rows / (splits * 2) >= 8) splits *= 2;
   p->db_row_splits = splits;
   return TRIFAST_OK;
 }
@@ -211,6 +219,8 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->neg_lse2 = (float*)(base + w.nlse_off);
   a->bias_t = w.has_bias_t ? (void*)(base + w.bias_t_off) : nullptr;
   a->rowfull = (uint8_t*)(base + w.rowfull_off);
+  a->maskbits = (uint32_t*)(base + w.maskbits_off);
+  a->mask_words = w.mask_words;
   a->db_f32 = (float*)(base + w.db_off);
   a->db_partials = (float*)(base + w.partial_off);
   a->splits = c.plan.db_row_splits;
@@ -308,7 +318,12 @@ int trifast_backward_db(const trifast_shape* shape, const trifast_t5* d_o, const
   a.db_f32 = db_f32;
   cudaStream_t s = (cudaStream_t)stream;
   if ((rc = cuda_rc(bwd_prepare(a, s)))) return rc;
-  if ((rc = cuda_rc(simt_bwd_db(a, s)))) return rc;
+  bool tc = c.plan.kernel == TRIFAST_KERNEL_TCGEN05;
+  if (tc && !tc_backward_supported(a)) {
+    if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
+    tc = false;
+  }
+  if ((rc = cuda_rc(tc ? tc_bwd_db(a, s) : simt_bwd_db(a, s)))) return rc;
   return cuda_rc(db_reduce_splits(a, s));
 }
 

@@ -24,6 +24,8 @@ struct BwdArgs {
   float* neg_lse2;       // (b, h, n_rows, n) fp32: -lse * log2(e), in the workspace
   void* bias_t;          // (b, h, k, j) transposed bias copy in the input dtype, or null
   uint8_t* rowfull;      // (b, n_rows): 1 = every key of the row is masked
+  uint32_t* maskbits;    // (b, n_rows, mask_words): bit set = key dropped or beyond n
+  int mask_words;        // 4 * ceil(n / 128)
   float* db_f32;         // (b, h, n, n) fp32 result of the row reduction
   float* db_partials;    // (splits, b, h, n, n) fp32, used when splits > 1
   int splits;
@@ -48,5 +50,6 @@ cudaError_t tc_forward(const FwdArgs& a, const trifast_plan& plan, cudaStream_t 
 bool tc_backward_supported(const BwdArgs& a);
 cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s);
 cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s);
+cudaError_t tc_bwd_db(const BwdArgs& a, cudaStream_t s);
 
 }  // namespace trifast

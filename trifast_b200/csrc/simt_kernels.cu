@@ -80,7 +80,8 @@ __device__ __forceinline__ void axpy_smem(float a, const float* sm, float* reg) 
 // ---------------------------------------------------------------------------
 // rowfull[b, i] = 1 when every key of pair row i is masked.
 // ---------------------------------------------------------------------------
-__global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowfull) {
+__global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowfull,
+                               uint32_t* maskbits, int mask_words) {
   const int bi = blockIdx.x;
   const int b = bi / n_rows, i = bi % n_rows;
   const uint8_t* row = mask.p + b * mask.sb + (int64_t)i * mask.si;
@@ -88,6 +89,14 @@ __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowful
   for (int k = threadIdx.x; k < n; k += blockDim.x) open |= (row[k] == 0);
   open = __syncthreads_or(open);
   if (threadIdx.x == 0) rowfull[bi] = open ? 0 : 1;
+  // Packed key mask (bit set = key dropped or beyond n).  A fully masked row
+  // keeps all n keys with uniform weight, so only the keys beyond n stay set.
+  for (int k0 = 0; k0 < mask_words * 32; k0 += blockDim.x) {
+    const int k = k0 + threadIdx.x;
+    const int dropped = (k < n) ? (open ? (row[k] != 0) : 0) : 1;
+    const unsigned bits = __ballot_sync(0xffffffffu, dropped);
+    if ((threadIdx.x & 31) == 0) maskbits[(int64_t)bi * mask_words + (k >> 5)] = bits;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -514,7 +523,8 @@ cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s) {
 
 cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
-  rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull);
+  rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
+                                                      a.mask_words);
   if (a.bias_t) {
     dim3 grid((dm.n + 31) / 32, (dm.n + 31) / 32, dm.batch * dm.heads);
     bias_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n);
