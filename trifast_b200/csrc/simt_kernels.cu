@@ -105,21 +105,42 @@ __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowful
 template <typename T, int D>
 __global__ void delta_kernel(View5 o, View5 d_o, const float* lse, float* delta, float* neg_lse2,
                              Dims dm) {
+  // A group of G threads owns one (b, h, i, j) row of D elements, 16 bytes per thread
+  // and step, so that a warp reads whole 128-byte lines of o and dO.
+  constexpr int kVec = 16 / sizeof(T);   // elements per 16-byte load
+  constexpr int G = (D / kVec) < 4 ? (D / kVec) : 4;
+  constexpr int kSteps = D / (kVec * G);
   const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const int j = idx % dm.n;
-  int64_t r = idx / dm.n;
-  const int i = r % dm.n_rows;
-  r /= dm.n_rows;
-  const int h = r % dm.heads, b = r / dm.heads;
-  const T* po = row5<T>(o, b, h, i, j);
-  const T* pd = row5<T>(d_o, b, h, i, j);
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t idx = gid / G;
+  const int part = (int)(gid % G);
+  const bool valid = idx < total;
   float acc = 0.f;
+  if (valid) {
+    const int j = idx % dm.n;
+    int64_t r = idx / dm.n;
+    const int i = r % dm.n_rows;
+    r /= dm.n_rows;
+    const int h = r % dm.heads, b = r / dm.heads;
+    const T* po = row5<T>(o, b, h, i, j);
+    const T* pd = row5<T>(d_o, b, h, i, j);
 #pragma unroll
-  for (int c = 0; c < D; ++c) acc = fmaf(to_f32<T>(po[c]), to_f32<T>(pd[c]), acc);
-  delta[idx] = acc;
-  neg_lse2[idx] = -lse[idx] * 1.4426950408889634f;
+    for (int st = 0; st < kSteps; ++st) {
+      const int off = (st * G + part) * kVec;
+      const uint4 uo = *reinterpret_cast<const uint4*>(po + off);
+      const uint4 ud = *reinterpret_cast<const uint4*>(pd + off);
+      const T* eo = reinterpret_cast<const T*>(&uo);
+      const T* ed = reinterpret_cast<const T*>(&ud);
+#pragma unroll
+      for (int c = 0; c < kVec; ++c) acc = fmaf(to_f32<T>(eo[c]), to_f32<T>(ed[c]), acc);
+    }
+  }
+#pragma unroll
+  for (int m = G / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (valid && part == 0) {
+    delta[idx] = acc;
+    neg_lse2[idx] = -lse[idx] * 1.4426950408889634f;
+  }
 }
 
 // bias_t[b, h, k, j] = bias[b, h, j, k] for 2-byte elements (the dk/dv kernel reads
@@ -532,9 +553,11 @@ cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
     using T = std::remove_pointer_t<decltype(tp)>;
     constexpr int D = decltype(dc)::value;
-    const int64_t total = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n;
-    delta_kernel<T, D><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(a.o, a.d_o, a.lse, a.delta,
-                                                                     a.neg_lse2, dm);
+    constexpr int kVec = 16 / sizeof(T);
+    constexpr int G = (D / kVec) < 4 ? (D / kVec) : 4;
+    const int64_t threads = (int64_t)dm.batch * dm.heads * dm.n_rows * dm.n * G;
+    delta_kernel<T, D><<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a.o, a.d_o, a.lse, a.delta,
+                                                                       a.neg_lse2, dm);
   });
 }
 

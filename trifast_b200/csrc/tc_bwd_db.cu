@@ -28,7 +28,11 @@ namespace {
 using namespace tc;
 
 constexpr float kLog2e = 1.4426950408889634f;
+// Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
+// the math warpgroups gain must not exceed what the issue warpgroup releases, or
+// the request blocks forever.
 constexpr int kRegsIssue = 56, kRegsMath = 224;
+static_assert(256 * kRegsMath + 128 * kRegsIssue <= 384 * 168, "setmaxnreg pool");
 
 template <int D, int NS>
 struct DbCfg {

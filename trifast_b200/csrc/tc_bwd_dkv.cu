@@ -14,8 +14,8 @@
 // the bias is read from a transposed copy (k-major) made by the prepare step, so
 // that a thread reads its row contiguously.
 //
-// Warps: 0 .. 4R-1 elementwise warpgroups, 4R TMA producer, 4R+1 MMA issuer,
-// 4R+2, 4R+3 idle.  TMEM columns per slot r (base r * 256): S^T [0,64),
+// Warps: 0 .. 4R-1 elementwise warpgroups, 4R TMA producer, 4R+1 .. 4R+R MMA issuers
+// (one per slot, so a slot never queues behind the other's waits), the rest idle.  TMEM columns per slot r (base r * 256): S^T [0,64),
 // dP^T [64,128), P^T [128,160), dS^T [160,192), dK [192, 192+D), dV [192+D, 192+2D)
 // (d = 64 runs one slot per CTA).
 //
@@ -35,7 +35,11 @@ using namespace tc;
 constexpr int kBKeys = 128, kBJ = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSmemLimit = 232448;
+// Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
+// the math warpgroups gain must not exceed what the issue warpgroup releases, or
+// the request blocks forever.
 constexpr int kRegsIssue = 56, kRegsMath = 224;
+static_assert(256 * kRegsMath + 128 * kRegsIssue <= 384 * 168, "setmaxnreg pool");
 
 template <int D, int R, int NS>
 struct DkvCfg {
@@ -63,8 +67,7 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
               const uint8_t* __restrict__ rowfull, MaskView mask, Dims dm, unsigned int* status) {
   using Cfg = DkvCfg<D, R, NS>;
   constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                P_READY = S_FREE + R, ACC_DONE = P_READY + R, TOKEN = ACC_DONE + R,
-                NBARS = TOKEN + R;
+                P_READY = S_FREE + R, ACC_DONE = P_READY + R, NBARS = ACC_DONE + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
   constexpr int kSlot = Cfg::kSlotCols;
 
@@ -114,7 +117,6 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(P_READY + r), 4);
       mbar_init(bar(ACC_DONE + r), 1);
-      mbar_init(bar(TOKEN + r), 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -161,13 +163,15 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           tma_load_4d(base + bias_off(s), &map_bt, bar(FULL + s), jt * kBJ, kt * kBKeys, h, b);
         }
       }
-    } else if (warp == 4 * R + 1) {
-      // ---------------------------------------------------------- MMA issuer
+    } else if (warp - (4 * R + 1) < nslots) {
+      // ---------------------------------------------------------- MMA issuers (one per slot)
+      const int r = warp - (4 * R + 1);
       if (lane == 0) {
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc_s = make_idesc(128, kBJ, kBf16, false, false);
         constexpr uint32_t idesc_acc = make_idesc(128, D, kBf16, false, true);
-        auto issue_s_dp = [&](int r, int s) {
+        auto issue_s_dp = [&](int r_, int s) {
+          const int r = r_;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t ak = make_smem_desc(k_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -185,42 +189,38 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
         if (ok) {
           tc_fence_after();
-          for (int r = 0; r < nslots; ++r) issue_s_dp(r, 0);
+          issue_s_dp(r, 0);
         }
         for (int jt = 0; jt < njt && ok; ++jt) {
           const int s = jt % NS;
           if (jt + 1 < njt) {
             const int ns = (jt + 1) % NS;
-            ok = mbar_wait(bar(FULL + ns), ((jt + 1) / NS) & 1, abort_flag);
-            for (int r = 0; r < nslots && ok; ++r) {
-              ok = mbar_wait(bar(S_FREE + r), jt & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue_s_dp(r, ns);
-            }
-          }
-          for (int r = 0; r < nslots && ok; ++r) {
-            ok = mbar_wait(bar(P_READY + r), jt & 1, abort_flag);
+            ok = mbar_wait(bar(FULL + ns), ((jt + 1) / NS) & 1, abort_flag) &&
+                 mbar_wait(bar(S_FREE + r), jt & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t acc = (jt > 0) ? 1u : 0u;
-#pragma unroll
-            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO
-              const uint64_t bd = make_smem_desc(do_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                                 Cfg::kSbo, Cfg::kSwz);
-              umma_ts(tmem_base + r * kSlot + 192 + D, tmem_base + r * kSlot + 128 + ks * 8, bd,
-                      idesc_acc, (ks > 0) ? 1u : acc);
-            }
-#pragma unroll
-            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dK += dS^T Q
-              const uint64_t bd = make_smem_desc(q_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                                 Cfg::kSbo, Cfg::kSwz);
-              umma_ts(tmem_base + r * kSlot + 192, tmem_base + r * kSlot + 160 + ks * 8, bd,
-                      idesc_acc, (ks > 0) ? 1u : acc);
-            }
-            umma_commit(bar(ACC_DONE + r));
-            umma_commit(bar(EMPTY + s));
+            issue_s_dp(r, ns);
           }
+          ok = mbar_wait(bar(P_READY + r), jt & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t acc = (jt > 0) ? 1u : 0u;
+#pragma unroll
+          for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO
+            const uint64_t bd = make_smem_desc(do_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                               Cfg::kSbo, Cfg::kSwz);
+            umma_ts(tmem_base + r * kSlot + 192 + D, tmem_base + r * kSlot + 128 + ks * 8, bd,
+                    idesc_acc, (ks > 0) ? 1u : acc);
+          }
+#pragma unroll
+          for (int ks = 0; ks < kBJ / 16; ++ks) {  // dK += dS^T Q
+            const uint64_t bd = make_smem_desc(q_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                               Cfg::kSbo, Cfg::kSwz);
+            umma_ts(tmem_base + r * kSlot + 192, tmem_base + r * kSlot + 160 + ks * 8, bd,
+                    idesc_acc, (ks > 0) ? 1u : acc);
+          }
+          umma_commit(bar(ACC_DONE + r));
+          umma_commit(bar(EMPTY + s));
         }
       }
     }
@@ -273,36 +273,50 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
         ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (jt / NS) & 1, abort_flag));
         if (!ok) break;
+        // One fused pass per 8 queries: bias^T / lse / delta loads, unpack, FMAs, the
+        // exponential, dS and both 16-bit packs, so that the LSU, ALU, FMA and MUFU
+        // pipes overlap inside one warp.
+        uint32_t pp[32], pd[32];
         {
           const uint8_t* brow = gbase + bias_off(s) + t * 128;
           const float4* lse4 = reinterpret_cast<const float4*>(gbase + lse_off(s, r));
           const float4* del4 = reinterpret_cast<const float4*>(gbase + delta_off(s, r));
 #pragma unroll
           for (int q8 = 0; q8 < 8; ++q8) {
-            const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
-            const float4 la = lse4[q8 * 2], lb = lse4[q8 * 2 + 1];
             const float4 da = del4[q8 * 2], db = del4[q8 * 2 + 1];
-            float b0, b1;
-            unpack2<T>(u.x, b0, b1);
-            x[q8 * 8 + 0] = fmaf(x[q8 * 8 + 0], c1, fmaf(b0, kLog2e, la.x));
-            x[q8 * 8 + 1] = fmaf(x[q8 * 8 + 1], c1, fmaf(b1, kLog2e, la.y));
-            unpack2<T>(u.y, b0, b1);
-            x[q8 * 8 + 2] = fmaf(x[q8 * 8 + 2], c1, fmaf(b0, kLog2e, la.z));
-            x[q8 * 8 + 3] = fmaf(x[q8 * 8 + 3], c1, fmaf(b1, kLog2e, la.w));
-            unpack2<T>(u.z, b0, b1);
-            x[q8 * 8 + 4] = fmaf(x[q8 * 8 + 4], c1, fmaf(b0, kLog2e, lb.x));
-            x[q8 * 8 + 5] = fmaf(x[q8 * 8 + 5], c1, fmaf(b1, kLog2e, lb.y));
-            unpack2<T>(u.w, b0, b1);
-            x[q8 * 8 + 6] = fmaf(x[q8 * 8 + 6], c1, fmaf(b0, kLog2e, lb.z));
-            x[q8 * 8 + 7] = fmaf(x[q8 * 8 + 7], c1, fmaf(b1, kLog2e, lb.w));
-            g[q8 * 8 + 0] -= da.x;
-            g[q8 * 8 + 1] -= da.y;
-            g[q8 * 8 + 2] -= da.z;
-            g[q8 * 8 + 3] -= da.w;
-            g[q8 * 8 + 4] -= db.x;
-            g[q8 * 8 + 5] -= db.y;
-            g[q8 * 8 + 6] -= db.z;
-            g[q8 * 8 + 7] -= db.w;
+            const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+            float p[8];
+            if (kMode == 2) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) p[e] = 0.f;
+            } else if (kMode == 3) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) p[e] = uniform;
+            } else {
+              const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
+              const float4 la = lse4[q8 * 2], lb = lse4[q8 * 2 + 1];
+              const float nl[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+              float bv[8];
+              unpack2<T>(u.x, bv[0], bv[1]);
+              unpack2<T>(u.y, bv[2], bv[3]);
+              unpack2<T>(u.z, bv[4], bv[5]);
+              unpack2<T>(u.w, bv[6], bv[7]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, nl[e])));
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const int c = q8 * 8 + e;
+              uint32_t wp = pack2<T>(p[e], p[e + 1]);
+              uint32_t wd = pack2<T>(p[e] * (g[c] - dl[e]), p[e + 1] * (g[c + 1] - dl[e + 1]));
+              if (kMode == 1 || kMode == 3) {  // dropped keys weigh exactly zero
+                wp = dropped ? 0u : wp;
+                wd = dropped ? 0u : wd;
+              }
+              pp[c >> 1] = wp;
+              pd[c >> 1] = wd;
+            }
           }
         }
         __syncwarp();
@@ -312,43 +326,8 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (jt - 1) & 1, abort_flag));
           if (!ok) break;
         }
-        if (R == 2 && nslots == 2) {  // the two slots alternate in the exp phase
-          ok = __all_sync(0xffffffffu,
-                          mbar_wait(bar(TOKEN + r), (r == 0) ? ((jt & 1) ^ 1) : (jt & 1), abort_flag));
-          if (!ok) break;
-        }
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t pp[16], pd[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int c = ch * 32 + e;
-            float p0, p1;
-            if (kMode == 2) {
-              p0 = 0.f;
-              p1 = 0.f;
-            } else if (kMode == 3) {
-              p0 = uniform;
-              p1 = uniform;
-            } else {
-              p0 = ex2(x[c]);
-              p1 = ex2(x[c + 1]);
-            }
-            uint32_t wp = pack2<T>(p0, p1), wd = pack2<T>(p0 * g[c], p1 * g[c + 1]);
-            if (kMode == 1 || kMode == 3) {  // dropped keys weigh exactly zero
-              wp = dropped ? 0u : wp;
-              wd = dropped ? 0u : wd;
-            }
-            pp[e >> 1] = wp;
-            pd[e >> 1] = wd;
-          }
-          tmem_st16(tP + ch * 16, pp);
-          tmem_st16(tDS + ch * 16, pd);
-        }
-        if (R == 2 && nslots == 2) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
-        }
+        tmem_st32(tP, pp);
+        tmem_st32(tDS, pd);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();

@@ -10,8 +10,8 @@
 // and at the end dq = dQ * d^-0.5.
 //
 // Warps: 0-7 two elementwise warpgroups (thread = query row), 8 TMA producer,
-// 9 MMA issuer, 10-11 idle (they complete the warpgroup whose registers are
-// handed over with setmaxnreg).  TMEM columns per slot r (base r * 256):
+// 9-10 MMA issuers (one per slot, so a slot never queues behind the other's waits),
+// 11 idle (it completes the warpgroup whose registers are handed over with setmaxnreg).  TMEM columns per slot r (base r * 256):
 // S [0,64), dP [64,128), dS [128,160) as 16-bit pairs, dQ [160, 160 + D).
 //
 // Stands in for `_bwd_q` of the reference (src/trifast/triton.py:268-383); delta
@@ -34,7 +34,11 @@ constexpr int kBJ = 128, kBK = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSmemLimit = 232448;
 constexpr int kHeaderBytes = 512;
+// Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
+// the math warpgroups gain must not exceed what the issue warpgroup releases, or
+// the request blocks forever.
 constexpr int kRegsIssue = 56, kRegsMath = 224;
+static_assert(256 * kRegsMath + 128 * kRegsIssue <= 384 * 168, "setmaxnreg pool");
 
 template <int D, int NS>
 struct DqCfg {
@@ -65,8 +69,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   using Cfg = DqCfg<D, NS>;
   constexpr int R = Cfg::R;
   constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                DS_READY = S_FREE + R, DQ_DONE = DS_READY + R, TOKEN = DQ_DONE + R,
-                NBARS = TOKEN + R;
+                DS_READY = S_FREE + R, DQ_DONE = DS_READY + R, NBARS = DQ_DONE + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
 
   extern __shared__ uint8_t smem_raw[];
@@ -112,7 +115,6 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(DS_READY + r), 4);
       mbar_init(bar(DQ_DONE + r), 1);
-      mbar_init(bar(TOKEN + r), 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -154,13 +156,15 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           tma_load_4d(base + bias_off(s), &map_b, bar(FULL + s), kt * kBK, jt * kBJ, h, b);
         }
       }
-    } else if (warp == 4 * R + 1) {
-      // ---------------------------------------------------------- MMA issuer
+    } else if (warp - (4 * R + 1) < nslots) {
+      // ---------------------------------------------------------- MMA issuers (one per slot)
+      const int r = warp - (4 * R + 1);
       if (lane == 0) {
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc_s = make_idesc(128, kBK, kBf16, false, false);
         constexpr uint32_t idesc_dq = make_idesc(128, D, kBf16, false, true);
-        auto issue_s_dp = [&](int r, int s) {
+        auto issue_s_dp = [&](int r_, int s) {
+          const int r = r_;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t aq = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -178,34 +182,30 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
         if (ok) {
           tc_fence_after();
-          for (int r = 0; r < nslots; ++r) issue_s_dp(r, 0);
+          issue_s_dp(r, 0);
         }
         for (int kt = 0; kt < nkt && ok; ++kt) {
           const int s = kt % NS;
           if (kt + 1 < nkt) {
             const int ns = (kt + 1) % NS;
-            ok = mbar_wait(bar(FULL + ns), ((kt + 1) / NS) & 1, abort_flag);
-            for (int r = 0; r < nslots && ok; ++r) {
-              ok = mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue_s_dp(r, ns);
-            }
-          }
-          for (int r = 0; r < nslots && ok; ++r) {
-            ok = mbar_wait(bar(DS_READY + r), kt & 1, abort_flag);
+            ok = mbar_wait(bar(FULL + ns), ((kt + 1) / NS) & 1, abort_flag) &&
+                 mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < kBK / 16; ++ks) {
-              const uint64_t bd = make_smem_desc(k_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                                 Cfg::kSbo, Cfg::kSwz);
-              umma_ts(tmem_base + r * 256 + 160, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_dq,
-                      (kt > 0 || ks > 0) ? 1u : 0u);
-            }
-            umma_commit(bar(DQ_DONE + r));
-            umma_commit(bar(EMPTY + s));
+            issue_s_dp(r, ns);
           }
+          ok = mbar_wait(bar(DS_READY + r), kt & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kBK / 16; ++ks) {
+            const uint64_t bd = make_smem_desc(k_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                               Cfg::kSbo, Cfg::kSwz);
+            umma_ts(tmem_base + r * 256 + 160, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_dq,
+                    (kt > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(bar(DQ_DONE + r));
+          umma_commit(bar(EMPTY + s));
         }
       }
     }
@@ -265,25 +265,38 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
           ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (kt / NS) & 1, abort_flag));
           if (!ok) break;
-          if (!kRowFull) {
-            const uint8_t* brow = gbase + bias_off(s) + t * 128;
+          // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
+          // exponential (MUFU), dS and the 16-bit pack, so that the pipes overlap
+          // inside one warp instead of running as separate phases.
+          uint32_t pk[32];
+          const uint8_t* brow = gbase + bias_off(s) + t * 128;
 #pragma unroll
-            for (int q8 = 0; q8 < 8; ++q8) {
+          for (int q8 = 0; q8 < 8; ++q8) {
+            float p[8];
+            if (kRowFull) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) p[e] = uniform;
+            } else {
               const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
-              float b0, b1;
-              unpack2<T>(u.x, b0, b1);
-              x[q8 * 8 + 0] = fmaf(x[q8 * 8 + 0], c1, fmaf(b0, kLog2e, neg_lse2));
-              x[q8 * 8 + 1] = fmaf(x[q8 * 8 + 1], c1, fmaf(b1, kLog2e, neg_lse2));
-              unpack2<T>(u.y, b0, b1);
-              x[q8 * 8 + 2] = fmaf(x[q8 * 8 + 2], c1, fmaf(b0, kLog2e, neg_lse2));
-              x[q8 * 8 + 3] = fmaf(x[q8 * 8 + 3], c1, fmaf(b1, kLog2e, neg_lse2));
-              unpack2<T>(u.z, b0, b1);
-              x[q8 * 8 + 4] = fmaf(x[q8 * 8 + 4], c1, fmaf(b0, kLog2e, neg_lse2));
-              x[q8 * 8 + 5] = fmaf(x[q8 * 8 + 5], c1, fmaf(b1, kLog2e, neg_lse2));
-              unpack2<T>(u.w, b0, b1);
-              x[q8 * 8 + 6] = fmaf(x[q8 * 8 + 6], c1, fmaf(b0, kLog2e, neg_lse2));
-              x[q8 * 8 + 7] = fmaf(x[q8 * 8 + 7], c1, fmaf(b1, kLog2e, neg_lse2));
+              float bv[8];
+              unpack2<T>(u.x, bv[0], bv[1]);
+              unpack2<T>(u.y, bv[2], bv[3]);
+              unpack2<T>(u.z, bv[4], bv[5]);
+              unpack2<T>(u.w, bv[6], bv[7]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, neg_lse2)));
             }
+            if (!clean) {
+              const uint32_t w = (q8 < 4) ? mw0 : mw1;
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if ((w >> ((q8 * 8 + e) & 31)) & 1u) p[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e += 2)
+              pk[(q8 * 8 + e) >> 1] = pack2<T>(p[e] * (g[q8 * 8 + e] - my_delta),
+                                               p[e + 1] * (g[q8 * 8 + e + 1] - my_delta));
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
@@ -291,33 +304,6 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
             ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (kt - 1) & 1, abort_flag));
             if (!ok) break;
-          }
-          if (nslots == 2) {  // the two slots alternate in the exp phase (see the forward)
-            ok = __all_sync(0xffffffffu,
-                            mbar_wait(bar(TOKEN + r), (r == 0) ? ((kt & 1) ^ 1) : (kt & 1), abort_flag));
-            if (!ok) break;
-          }
-          uint32_t pk[32];
-#pragma unroll
-          for (int c = 0; c < 64; c += 2) {
-            float p0, p1;
-            if (kRowFull) {
-              p0 = uniform;
-              p1 = uniform;
-            } else {
-              p0 = ex2(x[c]);
-              p1 = ex2(x[c + 1]);
-            }
-            if (!clean) {
-              const uint32_t w = (c < 32) ? mw0 : mw1;
-              if ((w >> (c & 31)) & 1u) p0 = 0.f;
-              if ((w >> ((c + 1) & 31)) & 1u) p1 = 0.f;
-            }
-            pk[c >> 1] = pack2<T>(p0 * (g[c] - my_delta), p1 * (g[c + 1] - my_delta));
-          }
-          if (nslots == 2) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
           }
           tmem_st32(tDS, pk);
           tmem_wait_st();

@@ -43,17 +43,49 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase: returns at once.  Used first in every wait, because
+// the potentially-blocking try_wait costs well over a hundred cycles even when
+// the phase has already completed.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Same test, but the hardware may park the thread for up to `hint_ns` while the
+// phase is incomplete, instead of returning at once: a waiting warp then issues
+// next to nothing and leaves the scheduler to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity,
+                                                     uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in these kernels is bounded: after kWaitCycles without the phase
 // completing (or as soon as another thread of the CTA has given up) the wait
 // returns false, the caller stops issuing work and the kernel drains and exits
 // with a status bit set; nothing traps and nothing spins forever.
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
+constexpr uint32_t kParkNs = 20000;              // re-check abort flag and clock every 20 us
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;

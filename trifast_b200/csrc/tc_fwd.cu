@@ -12,10 +12,11 @@
 //                     the row maximum moves, final O / l and lse
 //   warp 4R         : TMA producer (one lane): Q once, then K, V (per slot) and
 //                     the bias tile per key step through an NS-deep ring
-//   warp 4R + 1     : MMA issuer (one lane): S = Q K^T (SS, both operands K-major)
-//                     and O += P V (A = P from TMEM, B = V as an MN-major tile)
-//   warps 4R+2, 4R+3: idle; they complete the warpgroup so that its registers can
-//                     be handed to the softmax warpgroups (setmaxnreg)
+//   warps 4R+1, 4R+2: MMA issuers, one per slot (one lane each): S = Q K^T (SS,
+//                     both operands K-major) and O += P V (A = P from TMEM, B = V as
+//                     an MN-major tile); a slot's MMAs never wait behind the other's
+//   warp 4R + 3     : idle; it completes the warpgroup whose registers are handed
+//                     to the softmax warpgroups (setmaxnreg)
 //
 // TMEM columns per slot r (base r * 256): S [0,128) fp32, P [128,192) packed
 // 16-bit pairs, O [192, 192 + D) fp32.
@@ -47,7 +48,15 @@ using namespace tc;
 #define TRIFAST_REG_INC 224
 #endif
 
+// The hand-over must balance: 384 threads launch with 168 registers each, and a
+// request beyond what the issue warpgroup released would block forever.
+static_assert(256 * TRIFAST_REG_INC + 128 * TRIFAST_REG_DEC <= 384 * 168, "setmaxnreg pool");
+
 constexpr int kBJ = 128, kBK = 128;
+#ifndef TRIFAST_SLOT_TOKEN
+#define TRIFAST_SLOT_TOKEN 1
+#endif
+constexpr bool kSlotToken = TRIFAST_SLOT_TOKEN != 0;  // strict alternation of the slots' exp phases
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMaxInit = -1e30f;
@@ -175,13 +184,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tma_load_4d(bias_s + 16384, &map_b, bar(kFull + s), kt * kBK + 64, jt * kBJ, h, b);
       }
     }
-  } else if (warp == 4 * R + 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp - (4 * R + 1) < nslots) {
+    // ------------------------------------------------------------ MMA issuers (one per slot)
+    const int r = warp - (4 * R + 1);
     if (lane == 0) {
       constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBf16, false, true);
-      auto issue_qk = [&](int r, int s) {
+      auto issue_qk = [&](int r_, int s) {
+        const int r = r_;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t ad = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -190,37 +201,35 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         umma_commit(bar(S_FULL + r));
       };
+      // One issuing thread per slot: a slot's MMAs never queue behind a wait that
+      // belongs to the other slot.
       bool ok = mbar_wait(bar(kQFull), 0, abort_flag) && mbar_wait(bar(kFull), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        for (int r = 0; r < nslots; ++r) issue_qk(r, 0);
+        issue_qk(r, 0);
       }
       for (int kt = 0; kt < nkt && ok; ++kt) {
         const int s = kt % NS;
         if (kt + 1 < nkt) {
           const int ns = (kt + 1) % NS;
-          ok = mbar_wait(bar(kFull + ns), ((kt + 1) / NS) & 1, abort_flag);
-          for (int r = 0; r < nslots && ok; ++r) {
-            ok = mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(r, ns);
-          }
-        }
-        for (int r = 0; r < nslots && ok; ++r) {
-          ok = mbar_wait(bar(P_READY + r), kt & 1, abort_flag);
+          ok = mbar_wait(bar(kFull + ns), ((kt + 1) / NS) & 1, abort_flag) &&
+               mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < kBK / 16; ++ks) {
-            const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                               Cfg::kSbo, Cfg::kSwz);
-            umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
-                    (kt > 0 || ks > 0) ? 1u : 0u);
-          }
-          umma_commit(bar(O_DONE + r));
-          umma_commit(bar(EMPTY + s));
+          issue_qk(r, ns);
         }
+        ok = mbar_wait(bar(P_READY + r), kt & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kBK / 16; ++ks) {
+          const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                             Cfg::kSbo, Cfg::kSwz);
+          umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
+                  (kt > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(O_DONE + r));
+        umma_commit(bar(EMPTY + s));
       }
     }
   }
@@ -359,7 +368,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       // its own), so that one slot's loads, bias FMAs and maximum overlap the
       // other's exponentials instead of both phases running in lockstep.  Slot 0
       // goes first; each slot passes the turn on after issuing its exponentials.
-      if (R == 2 && nslots == 2) {
+      if (kSlotToken && R == 2 && nslots == 2) {
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bar(TOKEN + r), (r == 0) ? ((kt & 1) ^ 1) : (kt & 1), abort_flag));
         if (!ok) break;
@@ -387,7 +396,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tmem_st16(tP + ch * 16, pk);
       }
       l_run = fmaf(l_run, alpha, (sm[0] + sm[1]) + (sm[2] + sm[3]));
-      if (R == 2 && nslots == 2) {
+      if (kSlotToken && R == 2 && nslots == 2) {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
       }
