@@ -206,10 +206,12 @@ class DirectStep:
             self.adb = L.t4(self.db)
         plan = L.pick_plan(bs, h, n, rows, d, q.dtype)
         self.plan = plan
-        # launches per step: fwd 1; bwd: rowfull, delta, db, (split reduce), dq(+dkv), cast
+        # launches per step: forward 1; backward: row flags + packed mask, bias transpose
+        # (tensor-core path only), delta, db, split reduce (if split), dq, dk/dv, cast
         self.launches = 1
         if w.backward:
-            self.launches += 2 + 1 + (1 if plan["db_row_splits"] > 1 else 0) + 2 + 1
+            self.launches += 1 + (1 if plan["kernel"] == 2 else 0) + 1 + 1 + \
+                (1 if plan["db_row_splits"] > 1 else 0) + 2 + 1
 
     def forward(self):
         a, B = self.a, C.byref

@@ -96,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 // ------------------------------------------------------------------ TMA loads
 // Tiled loads global -> shared, completion counted in bytes on an mbarrier.
-// Never multicast: every CTA fetches its own tiles.
+// Every CTA fetches its own tiles (plain per-CTA loads only).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
