@@ -4,13 +4,14 @@
 // (a "row split"); it walks its rows, recomputing per row
 //     S  = Q_i K_i^T,   dP = dO_i V_i^T        (two SS MMAs, 128 x 128 each)
 //     P  = exp2(S * c + bias * log2e - lse_i * log2e),   dS = P * (dP - delta_i)
-// and sums dS in fp32 registers: thread = (query row j, 64-key half), 64
+// and sums dS in fp32 registers: thread = (query row j, 32-key quarter), 32
 // accumulators.  The partial of every row split is written as fp32 and the splits
 // are added in split order afterwards, so the result is deterministic: no atomics.
 //
-// Warps 0-3 and 4-7: elementwise warpgroups (key halves 0 and 1); warp 8 TMA
-// producer (Q, dO, K, V tiles and the -lse*log2e / delta vectors per row, NS-deep
-// ring); warp 9 MMA issuer; warps 10-11 idle.  TMEM: two buffers of S [0,128) and
+// Warps 0-15: four elementwise warpgroups, one per 32-key quarter of the tile, so
+// that four warps per scheduler cover each other's barrier, TMEM-load and MUFU
+// latencies; warp 16 TMA producer (Q, dO, K, V tiles and the -lse*log2e / delta
+// vectors per row, NS-deep ring); warp 17 MMA issuer; warps 18-19 idle.  TMEM: two buffers of S [0,128) and
 // dP [128,256), so the MMAs of row i+1 overlap the elementwise work of row i.
 //
 // Stands in for `_bwd_b` of the reference (src/trifast/triton.py:388-501), which
@@ -28,11 +29,13 @@ namespace {
 using namespace tc;
 
 constexpr float kLog2e = 1.4426950408889634f;
-// Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
-// the math warpgroups gain must not exceed what the issue warpgroup releases, or
-// the request blocks forever.
-constexpr int kRegsIssue = 56, kRegsMath = 224;
-static_assert(256 * kRegsMath + 128 * kRegsIssue <= 384 * 168, "setmaxnreg pool");
+// Register hand-over (setmaxnreg): 640 threads launch with 96 registers each; what
+// the math warpgroups gain must not exceed what the issue warpgroup releases (the
+// registers a CTA did not get at launch are not part of the pool), or the request
+// blocks forever.
+constexpr int kRegsLaunch = 96, kRegsIssue = 56, kRegsMath = 104;
+static_assert(512 * kRegsMath + 128 * kRegsIssue <= 640 * kRegsLaunch, "setmaxnreg pool");
+constexpr int kTmaWarp = 16, kMmaWarp = 17;
 
 template <int D, int NS>
 struct DbCfg {
@@ -40,14 +43,14 @@ struct DbCfg {
   static constexpr int kTileBytes = 128 * kRowBytes;
   static constexpr int kVecBytes = 128 * 4;
   static constexpr int kStageBytes = 4 * kTileBytes + 2 * kVecBytes;   // multiple of 1024
-  static constexpr int kThreads = 384;
+  static constexpr int kThreads = 640;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;
   static int smem_bytes() { return 1024 + 1024 + NS * kStageBytes; }
 };
 
 template <typename T, int D, int NS>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_nlse, const __grid_constant__ CUtensorMap map_delta,
@@ -92,20 +95,20 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar(FULL + s), 1);
-      mbar_init(bar(EMPTY + s), 1 + 8);  // MMA commit + 8 elementwise warps (vectors read)
+      mbar_init(bar(EMPTY + s), 1 + 16);  // MMA commit + 16 elementwise warps (vectors read)
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(bar(S_FULL + u), 1);
-      mbar_init(bar(S_FREE + u), 8);
+      mbar_init(bar(S_FREE + u), 16);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_do);
     tma_prefetch_desc(&map_k);
@@ -118,9 +121,9 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp >= 8) {
+  if (warp >= kTmaWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
-    if (warp == 8) {
+    if (warp == kTmaWarp) {
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
         for (int it = 0; it < nrows; ++it) {
@@ -135,7 +138,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           tma_load_4d(base + delta_off(s), &map_delta, bar(FULL + s), jt * 128, i, h, b);
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------- MMA issuer
       if (lane == 0) {
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -167,29 +170,33 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
     // ------------------------------------------------------------ elementwise warpgroups
-    const int half = warp >> 2, wq = warp & 3, row = tid & 127;
+    const int quarter = warp >> 2, wq = warp & 3, row = tid & 127;
     const int j = jt * 128 + row;
-    const int key0 = kt * 128 + half * 64;
+    const int key0 = kt * 128 + quarter * 32;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const float c1 = dm.scale * kLog2e;
     const float uniform = 1.f / (float)n;
 
-    float acc[64], bl[64];
+    float acc[32];
+    uint32_t bp[16];  // this thread's 32 bias values, kept as 16-bit pairs
     {
       const T* brow = reinterpret_cast<const T*>(bias.p) + b * bias.sb + h * bias.sh +
                       (int64_t)min(j, n - 1) * bias.sj;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; c += 2) {
         acc[c] = 0.f;
-        bl[c] = (key0 + c < n) ? to_f32<T>(brow[key0 + c]) * kLog2e : 0.f;
+        acc[c + 1] = 0.f;
+        const float b0 = (key0 + c < n) ? to_f32<T>(brow[key0 + c]) : 0.f;
+        const float b1 = (key0 + c + 1 < n) ? to_f32<T>(brow[key0 + c + 1]) : 0.f;
+        bp[c >> 1] = pack2<T>(b0, b1);  // exact: the values are 16-bit already
       }
     }
     bool ok = true;
     for (int it = 0; it < nrows; ++it) {
       const int s = it % NS, u = it & 1, i = i_begin + it;
       // per-row inputs that do not come through shared memory
-      const uint32_t* mrow = maskbits + ((int64_t)b * dm.n_rows + i) * mask_words + kt * 4 + half * 2;
-      const uint32_t mw0 = __ldg(mrow), mw1 = __ldg(mrow + 1);
+      const uint32_t mw =
+          __ldg(maskbits + ((int64_t)b * dm.n_rows + i) * mask_words + kt * 4 + quarter);
       const bool row_full = rowfull[b * dm.n_rows + i] != 0;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (it / NS) & 1, abort_flag));
       if (!ok) break;
@@ -200,49 +207,52 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + u), (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tmem_base + lane_base + u * 256 + half * 64;
+      const uint32_t tS = tmem_base + lane_base + u * 256 + quarter * 32;
       const uint32_t tDP = tS + 128;
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
-        float x[32], g[32];
-        tmem_ld32(tS + hc * 32, reinterpret_cast<uint32_t*>(x));
-        tmem_ld32(tDP + hc * 32, reinterpret_cast<uint32_t*>(g));
+        float x[16], g[16];
+        tmem_ld16(tS + hc * 16, reinterpret_cast<uint32_t*>(x));
+        tmem_ld16(tDP + hc * 16, reinterpret_cast<uint32_t*>(g));
         tmem_wait_ld();
-        const uint32_t mw = hc ? mw1 : mw0;
+        if (hc == 1) {  // everything this warp needs from the buffer is in registers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(S_FREE + u));
+        }
+        const uint32_t mh = (mw >> (hc * 16)) & 0xffffu;
         if (row_full) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float p = ((mw >> c) & 1u) ? 0.f : uniform;
-            acc[hc * 32 + c] = fmaf(p, g[c] - dl, acc[hc * 32 + c]);
-          }
-        } else if (mw == 0u) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float p = ex2(fmaf(x[c], c1, bl[hc * 32 + c]) + nl);
-            acc[hc * 32 + c] = fmaf(p, g[c] - dl, acc[hc * 32 + c]);
+          for (int c = 0; c < 16; ++c) {
+            const float p = ((mh >> c) & 1u) ? 0.f : uniform;
+            acc[hc * 16 + c] = fmaf(p, g[c] - dl, acc[hc * 16 + c]);
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            float p = ex2(fmaf(x[c], c1, bl[hc * 32 + c]) + nl);
-            if ((mw >> c) & 1u) p = 0.f;
-            acc[hc * 32 + c] = fmaf(p, g[c] - dl, acc[hc * 32 + c]);
+          for (int c = 0; c < 16; c += 2) {
+            float b0, b1;
+            unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
+            float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
+            float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
+            if (mh != 0u) {
+              if ((mh >> c) & 1u) p0 = 0.f;
+              if ((mh >> (c + 1)) & 1u) p1 = 0.f;
+            }
+            acc[hc * 16 + c] = fmaf(p0, g[c] - dl, acc[hc * 16 + c]);
+            acc[hc * 16 + c + 1] = fmaf(p1, g[c + 1] - dl, acc[hc * 16 + c + 1]);
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(S_FREE + u));
     }
     if (ok && j < n) {
       float* dst = out + (((int64_t)split * dm.batch * dm.heads + bh) * n + j) * n + key0;
-      if (key0 + 64 <= n) {
+      if (key0 + 32 <= n) {
 #pragma unroll
-        for (int c = 0; c < 64; c += 4)
+        for (int c = 0; c < 32; c += 4)
           *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
       } else {
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
+        for (int c = 0; c < 32; ++c)
           if (key0 + c < n) dst[c] = acc[c];
       }
     }
@@ -258,7 +268,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     if (tid == 0) atomicOr(status, (unsigned int)kStatusTimeoutBwdDb);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
