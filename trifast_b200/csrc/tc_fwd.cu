@@ -1,17 +1,19 @@
 // Forward triangle attention on the 5th-generation tensor cores (bf16 / fp16).
 //
-// One CTA owns a 128-query tile (h, j-tile) of R consecutive pair rows i ("slots")
-// and walks the keys in tiles of 128.  The R slots share every bias tile, which
-// is the dominant shared-memory stream (32 KiB per step against 8-16 KiB of K+V
-// per slot), and give the tensor pipe independent work while the softmax of the
-// other slot runs.
+// Work item = one 128-query tile (h, j-tile) of R = 2 consecutive pair rows i
+// ("slots"), walked over the keys in tiles of 128.  The slots share every bias
+// tile, which is the dominant shared-memory stream (32 KiB per step against
+// 8-16 KiB of K+V per slot), and give the tensor pipe independent work while the
+// softmax of the other slot runs.  CTAs are persistent: one per SM, each looping
+// over work items, so that the loads and the first MMA of the next item overlap
+// the tail of the current one instead of paying a pipeline fill per item.
 //
 //   warps 0 .. 4R-1 : softmax warpgroups, one per slot; thread t owns query row t:
 //                     S (TMEM) -> registers, + bias (shared memory), mask, online
 //                     softmax in fp32, P -> TMEM as 16-bit pairs, O rescale when
 //                     the row maximum moves, final O / l and lse
-//   warp 4R         : TMA producer (one lane): Q once, then K, V (per slot) and
-//                     the bias tile per key step through an NS-deep ring
+//   warp 4R         : TMA producer (one lane): Q per item, then K, V (per slot)
+//                     and the bias tile per key step through an NS-deep ring
 //   warps 4R+1, 4R+2: MMA issuers, one per slot (one lane each): S = Q K^T (SS,
 //                     both operands K-major) and O += P V (A = P from TMEM, B = V as
 //                     an MN-major tile); a slot's MMAs never wait behind the other's
@@ -39,27 +41,28 @@ namespace {
 using namespace tc;
 
 // Registers per thread after the warpgroups rebalance (setmaxnreg): the last
-// warpgroup drops to kRegsIssue, the softmax warpgroups rise to kRegsSoftmax;
-// 2 * 128 * 224 + 128 * 56 = 64512 <= 65536.
+// warpgroup drops to TRIFAST_REG_DEC, the softmax warpgroups rise to
+// TRIFAST_REG_INC.  The hand-over must balance: 384 threads launch with 168
+// registers each, and a request beyond what the issue warpgroup released would
+// block forever.
 #ifndef TRIFAST_REG_DEC
 #define TRIFAST_REG_DEC 56
 #endif
 #ifndef TRIFAST_REG_INC
 #define TRIFAST_REG_INC 224
 #endif
-
-// The hand-over must balance: 384 threads launch with 168 registers each, and a
-// request beyond what the issue warpgroup released would block forever.
 static_assert(256 * TRIFAST_REG_INC + 128 * TRIFAST_REG_DEC <= 384 * 168, "setmaxnreg pool");
 
 constexpr int kBJ = 128, kBK = 128;
-#ifndef TRIFAST_SLOT_TOKEN
-#define TRIFAST_SLOT_TOKEN 1
-#endif
-constexpr bool kSlotToken = TRIFAST_SLOT_TOKEN != 0;  // strict alternation of the slots' exp phases
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMaxInit = -1e30f;
+// A tile moves the running maximum only when it exceeds it by more than kLazyTau
+// (natural-log units).  0 = always track the exact maximum: the largest weight of a
+// row is then exactly 1 before rounding to 16 bits, which keeps the error of peaked
+// rows lowest; a positive value (FlashAttention-style lazy rescale) trades that for
+// fewer rescales of O.
+constexpr float kLazyTau = 0.f;
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in limit per CTA
 constexpr int kHeaderBytes = 512;
 
@@ -73,24 +76,31 @@ struct FwdCfg {
   static constexpr int kThreads = R * 128 + 128;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
+  // per softmax warp: 4 mask words per 128-key chunk
+  static int mask_bytes(int n) { return 4 * R * ((n + kBK - 1) / kBK) * 16; }
   static int smem_bytes(int n) {
-    const int nkt = (n + kBK - 1) / kBK;
-    const int head = (kHeaderBytes + R * nkt * 16 + 1023) / 1024 * 1024;
+    const int head = (kHeaderBytes + mask_bytes(n) + 1023) / 1024 * 1024;
     return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
   }
 };
 
-enum BarIdx { kQFull = 0, kFull = 1 };
+// Work items in launch order: j-tile fastest, then row pair, then (b, h): the CTAs
+// running at one time share bias strips and K/V rows in L2.
+struct ItemGrid {
+  int njt, nrp, total;
+};
 
 template <typename T, int D, int R, int NS>
 __global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
-              View5 o, float* __restrict__ lse, MaskView mask, Dims dm, unsigned int* status) {
+              View5 o, float* __restrict__ lse, MaskView mask, Dims dm, ItemGrid items,
+              unsigned int* status) {
   using Cfg = FwdCfg<D, R, NS>;
-  constexpr int EMPTY = kFull + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                P_READY = S_FREE + R, O_DONE = P_READY + R, TOKEN = O_DONE + R,
-                NBARS = TOKEN + R;
+  static_assert(R == 2, "two slots: the exp phases alternate between them");
+  constexpr int Q_FULL = 0, Q_EMPTY = 1, FULL = 2, EMPTY = FULL + NS, S_FULL = EMPTY + NS,
+                S_FREE = S_FULL + R, P_READY = S_FREE + R, O_DONE = P_READY + R,
+                O_FREE = O_DONE + R, TOKEN = O_FREE + R, NBARS = TOKEN + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
 
   extern __shared__ uint8_t smem_raw[];
@@ -99,12 +109,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint8_t* gbase = smem_raw + (base - raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
-  int* open_flag = reinterpret_cast<int*>(gbase + 264);           // [R]
-  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [R][nkt][4]
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][nkt][4]
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
-  const uint32_t tiles_off = (kHeaderBytes + R * nkt * 16 + 1023u) & ~1023u;
+  const uint32_t tiles_off = (kHeaderBytes + 4 * R * nkt * 16 + 1023u) & ~1023u;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kTileBytes; };
@@ -118,29 +127,43 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   auto bias_off = [&](int s) -> uint32_t {  // byte offset from gbase
     return tiles_off + R * Cfg::kTileBytes + s * Cfg::kStageBytes + 2 * R * Cfg::kTileBytes;
   };
+  // item -> (j tile, first row, head, batch); a slot beyond the last row re-does the
+  // last row (its loads stay in range, its results are not stored)
+  struct Item {
+    int jt, i0, h, b;
+  };
+  auto decode = [&](int w) -> Item {
+    Item it;
+    it.jt = w % items.njt;
+    const int rest = w / items.njt;
+    it.i0 = (rest % items.nrp) * R;
+    const int bh = rest / items.nrp;
+    it.h = bh % dm.heads;
+    it.b = bh / dm.heads;
+    return it;
+  };
+  auto slot_row = [&](const Item& it, int r) -> int { return min(it.i0 + r, dm.n_rows - 1); };
 
   // A wait that gave up in an earlier CTA or launch leaves the status word set:
   // stop doing work until the host has read and cleared it.
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int jt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
-  const int b = bh / dm.heads, h = bh % dm.heads;
-  const int nslots = min(R, dm.n_rows - i0);
 
   if (tid == 0) {
-    mbar_init(bar(kQFull), 1);
+    mbar_init(bar(Q_FULL), 1);
+    mbar_init(bar(Q_EMPTY), R);
     for (int s = 0; s < NS; ++s) {
-      mbar_init(bar(kFull + s), 1);
-      mbar_init(bar(EMPTY + s), nslots * 5);  // per slot: 1 MMA commit + 4 softmax warps
+      mbar_init(bar(FULL + s), 1);
+      mbar_init(bar(EMPTY + s), R * 5);  // per slot: 1 MMA commit + 4 softmax warps
     }
     for (int r = 0; r < R; ++r) {
       mbar_init(bar(S_FULL + r), 1);
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(P_READY + r), 4);
       mbar_init(bar(O_DONE + r), 1);
+      mbar_init(bar(O_FREE + r), 4);
       mbar_init(bar(TOKEN + r), 4);
-      open_flag[r] = 0;
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -160,39 +183,43 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Register budget: the last warpgroup (producer, MMA issuer, two idle warps)
-  // hands most of its registers to the softmax warpgroups, which keep a whole
-  // 128-column score row per thread.
   if (warp >= 4 * R) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TRIFAST_REG_DEC));
   if (warp == 4 * R) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(kQFull), nslots * Cfg::kTileBytes);
-      for (int r = 0; r < nslots; ++r)
-        tma_load_5d(q_tile(r), &map_q, bar(kQFull), 0, jt * kBJ, i0 + r, h, b);
-      for (int kt = 0; kt < nkt; ++kt) {
-        const int s = kt % NS;
-        if (kt >= NS && !mbar_wait(bar(EMPTY + s), ((kt / NS) - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(bar(kFull + s), nslots * 2 * Cfg::kTileBytes + Cfg::kBiasBytes);
-        for (int r = 0; r < nslots; ++r) {
-          tma_load_5d(k_tile(s, r), &map_k, bar(kFull + s), 0, kt * kBK, i0 + r, h, b);
-          tma_load_5d(v_tile(s, r), &map_v, bar(kFull + s), 0, kt * kBK, i0 + r, h, b);
+      int g = 0, it = 0;  // running key-tile and item counters (barrier phases)
+      bool ok = true;
+      for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+        const Item im = decode(w);
+        if (it > 0) ok = mbar_wait(bar(Q_EMPTY), (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar(Q_FULL), R * Cfg::kTileBytes);
+        for (int r = 0; r < R; ++r)
+          tma_load_5d(q_tile(r), &map_q, bar(Q_FULL), 0, im.jt * kBJ, slot_row(im, r), im.h, im.b);
+        for (int kt = 0; kt < nkt; ++kt, ++g) {
+          const int s = g % NS;
+          if (g >= NS) ok = mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(FULL + s), R * 2 * Cfg::kTileBytes + Cfg::kBiasBytes);
+          for (int r = 0; r < R; ++r) {
+            tma_load_5d(k_tile(s, r), &map_k, bar(FULL + s), 0, kt * kBK, slot_row(im, r), im.h, im.b);
+            tma_load_5d(v_tile(s, r), &map_v, bar(FULL + s), 0, kt * kBK, slot_row(im, r), im.h, im.b);
+          }
+          const uint32_t bias_s = base + bias_off(s);
+          tma_load_4d(bias_s, &map_b, bar(FULL + s), kt * kBK, im.jt * kBJ, im.h, im.b);
+          tma_load_4d(bias_s + 16384, &map_b, bar(FULL + s), kt * kBK + 64, im.jt * kBJ, im.h, im.b);
         }
-        const uint32_t bias_s = base + bias_off(s);
-        tma_load_4d(bias_s, &map_b, bar(kFull + s), kt * kBK, jt * kBJ, h, b);
-        tma_load_4d(bias_s + 16384, &map_b, bar(kFull + s), kt * kBK + 64, jt * kBJ, h, b);
       }
     }
-  } else if (warp - (4 * R + 1) < nslots) {
+  } else if (warp - (4 * R + 1) < R) {
     // ------------------------------------------------------------ MMA issuers (one per slot)
     const int r = warp - (4 * R + 1);
     if (lane == 0) {
       constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBf16, false, true);
-      auto issue_qk = [&](int r_, int s) {
-        const int r = r_;
+      auto issue_qk = [&](int s) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t ad = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -201,239 +228,262 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         umma_commit(bar(S_FULL + r));
       };
-      // One issuing thread per slot: a slot's MMAs never queue behind a wait that
-      // belongs to the other slot.
-      bool ok = mbar_wait(bar(kQFull), 0, abort_flag) && mbar_wait(bar(kFull), 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(r, 0);
-      }
-      for (int kt = 0; kt < nkt && ok; ++kt) {
-        const int s = kt % NS;
-        if (kt + 1 < nkt) {
-          const int ns = (kt + 1) % NS;
-          ok = mbar_wait(bar(kFull + ns), ((kt + 1) / NS) & 1, abort_flag) &&
-               mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          issue_qk(r, ns);
-        }
-        ok = mbar_wait(bar(P_READY + r), kt & 1, abort_flag);
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+        // S of the item's first key tile: needs Q, the first stage, and the S columns
+        // released by the softmax of the previous item's last tile
+        ok = mbar_wait(bar(Q_FULL), it & 1, abort_flag) &&
+             mbar_wait(bar(FULL + g % NS), (g / NS) & 1, abort_flag) &&
+             (g == 0 || mbar_wait(bar(S_FREE + r), (g - 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
+        issue_qk(g % NS);
+        if (nkt == 1) umma_commit(bar(Q_EMPTY));
+        for (int kt = 0; kt < nkt && ok; ++kt, ++g) {
+          const int s = g % NS;
+          if (kt + 1 < nkt) {
+            const int ns = (g + 1) % NS;
+            ok = mbar_wait(bar(FULL + ns), ((g + 1) / NS) & 1, abort_flag) &&
+                 mbar_wait(bar(S_FREE + r), g & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(ns);
+            if (kt + 2 == nkt) umma_commit(bar(Q_EMPTY));  // last read of this item's Q tile
+          }
+          ok = mbar_wait(bar(P_READY + r), g & 1, abort_flag);
+          // the first PV of an item overwrites O: the previous item's epilogue must have read it
+          if (ok && kt == 0 && it > 0) ok = mbar_wait(bar(O_FREE + r), (it - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks) {
-          const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                             Cfg::kSbo, Cfg::kSwz);
-          umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
-                  (kt > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < kBK / 16; ++ks) {
+            const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                               Cfg::kSbo, Cfg::kSwz);
+            umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
+                    (kt > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(bar(O_DONE + r));
+          umma_commit(bar(EMPTY + s));
         }
-        umma_commit(bar(O_DONE + r));
-        umma_commit(bar(EMPTY + s));
       }
     }
   }
   } else {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TRIFAST_REG_INC));
-  if (warp / 4 < nslots) {
-    // ------------------------------------------------------------ softmax warpgroup
+  {
+    // ------------------------------------------------------------ softmax warpgroups
     const int r = warp / 4, wq = warp & 3, t = tid & 127;
-    const int i = i0 + r;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + r * 256;
     const uint32_t tP = tS + 128, tO = tS + 192;
-    uint32_t* mb = maskbits + r * nkt * 4;
+    uint32_t* mb = maskbits + warp * nkt * 4;  // this warp's own copy: no cross-warp sync
 
-    {  // key mask of row i as bit words; bit set = key dropped (or beyond n)
-      const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
-      int any_open = 0;
-      for (int kt = 0; kt < nkt; ++kt) {
-        const int key = kt * kBK + t;
-        const int dropped = (key < n) ? (mrow[key] != 0) : 1;
-        any_open |= (key < n) && !dropped;
-        const uint32_t bits = __ballot_sync(0xffffffffu, dropped);
-        if (lane == 0) mb[kt * 4 + wq] = bits;
-      }
-      if (__any_sync(0xffffffffu, any_open) && lane == 0) atomicOr(&open_flag[r], 1);
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
-    }
-    const bool row_full = open_flag[r] == 0;
-
-    float m_run = kMaxInit, l_run = 0.f;
+    int g = 0, it = 0;
     bool ok = true;
-    // The key loop exists in two copies, chosen once per row: the fully-masked-row
-    // case (every score is 0) must not merge with the regular case inside the
-    // loop, or the 128 live scores get duplicated and spill.
-    auto key_loop = [&](auto row_full_tag) {
-    constexpr bool kRowFull = decltype(row_full_tag)::value;
-    for (int kt = 0; kt < nkt; ++kt) {
-      const int s = kt % NS;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), kt & 1, abort_flag));
-      if (!ok) break;
-      tc_fence_after();
-      float x[128];
+    for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+      const Item im = decode(w);
+      const int i = slot_row(im, r);
+      const bool do_store = im.i0 + r < dm.n_rows;
+      const int b = im.b, h = im.h, jt = im.jt;
+
+      // Key mask of row i as bit words (bit set = key dropped or beyond n).  Lane l
+      // reads keys 4l .. 4l+3 of a 128-key chunk as one word; word j of the chunk
+      // then holds, at bit l, key 4l + j.
+      bool row_full;
       {
-        uint32_t* xr = reinterpret_cast<uint32_t*>(x);
-        tmem_ld32(tS + 0, xr + 0);
-        tmem_ld32(tS + 32, xr + 32);
-        tmem_ld32(tS + 64, xr + 64);
-        tmem_ld32(tS + 96, xr + 96);
-        tmem_wait_ld();
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(S_FREE + r));
-
-      // mask words of this key tile (uniform over the warpgroup)
-      uint32_t mw[4];
+        const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+        uint32_t open = 0;
+        for (int c = 0; c < nkt; ++c) {
+          const int key4 = c * kBK + 4 * lane;
+          const bool valid = key4 < n;
+          const uint32_t u = valid ? __ldg(reinterpret_cast<const uint32_t*>(mrow + key4)) : 0x01010101u;
+          const uint32_t vm = __ballot_sync(0xffffffffu, valid);
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        if (kRowFull) {  // only keys beyond n stay dropped
-          const int valid = n - (kt * kBK + 32 * w);
-          mw[w] = valid >= 32 ? 0u : (valid <= 0 ? 0xffffffffu : ~((1u << valid) - 1u));
-        } else {
-          mw[w] = mb[kt * 4 + w];
-        }
-      }
-      const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
-
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(kFull + s), (kt / NS) & 1, abort_flag));
-      if (!ok) break;
-      if (kRowFull) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) x[c] = 0.f;
-      } else {
-        const uint8_t* brow = gbase + bias_off(s) + t * 128;
-#pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const uint4 u = *reinterpret_cast<const uint4*>(brow + (g >> 3) * 16384 +
-                                                          (((g & 7) ^ (t & 7)) << 4));
-          float b0, b1;
-          unpack2<T>(u.x, b0, b1);
-          x[g * 8 + 0] = fmaf(x[g * 8 + 0], dm.scale, b0);
-          x[g * 8 + 1] = fmaf(x[g * 8 + 1], dm.scale, b1);
-          unpack2<T>(u.y, b0, b1);
-          x[g * 8 + 2] = fmaf(x[g * 8 + 2], dm.scale, b0);
-          x[g * 8 + 3] = fmaf(x[g * 8 + 3], dm.scale, b1);
-          unpack2<T>(u.z, b0, b1);
-          x[g * 8 + 4] = fmaf(x[g * 8 + 4], dm.scale, b0);
-          x[g * 8 + 5] = fmaf(x[g * 8 + 5], dm.scale, b1);
-          unpack2<T>(u.w, b0, b1);
-          x[g * 8 + 6] = fmaf(x[g * 8 + 6], dm.scale, b0);
-          x[g * 8 + 7] = fmaf(x[g * 8 + 7], dm.scale, b1);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
-
-      if (!clean) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if ((mw[c >> 5] >> (c & 31)) & 1u) x[c] = -INFINITY;
-      }
-      // Four independent chains for the row maximum and the row sum: with two
-      // warps per scheduler a single dependent chain of 128 would be latency-bound.
-      float mx[4] = {x[0], x[1], x[2], x[3]};
-#pragma unroll
-      for (int c = 4; c < 128; c += 4) {
-        mx[0] = fmaxf(mx[0], x[c + 0]);
-        mx[1] = fmaxf(mx[1], x[c + 1]);
-        mx[2] = fmaxf(mx[2], x[c + 2]);
-        mx[3] = fmaxf(mx[3], x[c + 3]);
-      }
-      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_run, mt);
-      const float neg = -m_new * kLog2e;
-      const float alpha = ex2(fmaf(m_run, kLog2e, neg));
-      m_run = m_new;
-
-      if (kt > 0) {
-        // PV of the previous key tile must be done before O is rescaled and P reused.
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (kt - 1) & 1, abort_flag));
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t acc[32];
-            tmem_ld32(tO + 32 * c, acc);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-            tmem_st32(tO + 32 * c, acc);
+          for (int jb = 0; jb < 4; ++jb) {
+            const uint32_t bits = __ballot_sync(0xffffffffu, ((u >> (8 * jb)) & 0xffu) != 0u);
+            if (lane == 0) mb[c * 4 + jb] = bits;
+            open |= ~bits & vm;
           }
         }
+        __syncwarp();
+        row_full = open == 0u;
       }
-      // The two slots take turns in the exp phase (it saturates the MUFU pipe on
-      // its own), so that one slot's loads, bias FMAs and maximum overlap the
-      // other's exponentials instead of both phases running in lockstep.  Slot 0
-      // goes first; each slot passes the turn on after issuing its exponentials.
-      if (kSlotToken && R == 2 && nslots == 2) {
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(bar(TOKEN + r), (r == 0) ? ((kt & 1) ^ 1) : (kt & 1), abort_flag));
+
+      float m_run = kMaxInit, l_run = 0.f;
+      // The key loop exists in two copies, chosen once per row: the fully-masked-row
+      // case (every score is 0) must not merge with the regular case inside the
+      // loop, or the 128 live scores get duplicated and spill.
+      auto key_loop = [&](auto row_full_tag) {
+      constexpr bool kRowFull = decltype(row_full_tag)::value;
+      for (int kt = 0; kt < nkt; ++kt, ++g) {
+        const int s = g % NS;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
         if (!ok) break;
-      }
-      // exp and P store in chunks of 32 keys, so a packed chunk leaves the
-      // registers as soon as it is made; four independent partial sums.
-      float sm[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const int c = ch * 32 + e;
-          const float p0 = ex2(fmaf(x[c + 0], kLog2e, neg));
-          const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
-          const float p2 = ex2(fmaf(x[c + 2], kLog2e, neg));
-          const float p3 = ex2(fmaf(x[c + 3], kLog2e, neg));
-          sm[0] += p0;
-          sm[1] += p1;
-          sm[2] += p2;
-          sm[3] += p3;
-          pk[(e >> 1) + 0] = pack2<T>(p0, p1);
-          pk[(e >> 1) + 1] = pack2<T>(p2, p3);
+        tc_fence_after();
+        float x[128];
+        {
+          uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+          tmem_ld32(tS + 0, xr + 0);
+          tmem_ld32(tS + 32, xr + 32);
+          tmem_ld32(tS + 64, xr + 64);
+          tmem_ld32(tS + 96, xr + 96);
+          tmem_wait_ld();
         }
-        tmem_st16(tP + ch * 16, pk);
-      }
-      l_run = fmaf(l_run, alpha, (sm[0] + sm[1]) + (sm[2] + sm[3]));
-      if (kSlotToken && R == 2 && nslots == 2) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_FREE + r));
+
+        // mask words of this key tile (uniform over the warp); column c of the tile
+        // is bit (c >> 2) of word (c & 3)
+        uint32_t mw[4];
+#pragma unroll
+        for (int jb = 0; jb < 4; ++jb) {
+          if (kRowFull) {  // only keys beyond n stay dropped
+            const int groups = (n - kt * kBK) / 4;
+            mw[jb] = groups >= 32 ? 0u : (groups <= 0 ? 0xffffffffu : ~((1u << groups) - 1u));
+          } else {
+            mw[jb] = mb[kt * 4 + jb];
+          }
+        }
+        const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
+
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
+        if (!ok) break;
+        if (kRowFull) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) x[c] = 0.f;
+        } else {
+          const uint8_t* brow = gbase + bias_off(s) + t * 128;
+#pragma unroll
+          for (int gq = 0; gq < 16; ++gq) {
+            const uint4 u = *reinterpret_cast<const uint4*>(brow + (gq >> 3) * 16384 +
+                                                            (((gq & 7) ^ (t & 7)) << 4));
+            float b0, b1;
+            unpack2<T>(u.x, b0, b1);
+            x[gq * 8 + 0] = fmaf(x[gq * 8 + 0], dm.scale, b0);
+            x[gq * 8 + 1] = fmaf(x[gq * 8 + 1], dm.scale, b1);
+            unpack2<T>(u.y, b0, b1);
+            x[gq * 8 + 2] = fmaf(x[gq * 8 + 2], dm.scale, b0);
+            x[gq * 8 + 3] = fmaf(x[gq * 8 + 3], dm.scale, b1);
+            unpack2<T>(u.z, b0, b1);
+            x[gq * 8 + 4] = fmaf(x[gq * 8 + 4], dm.scale, b0);
+            x[gq * 8 + 5] = fmaf(x[gq * 8 + 5], dm.scale, b1);
+            unpack2<T>(u.w, b0, b1);
+            x[gq * 8 + 6] = fmaf(x[gq * 8 + 6], dm.scale, b0);
+            x[gq * 8 + 7] = fmaf(x[gq * 8 + 7], dm.scale, b1);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+
+        if (!clean) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            if ((mw[c & 3] >> (c >> 2)) & 1u) x[c] = -INFINITY;
+        }
+        // Four independent chains for the row maximum and the row sum: with two
+        // warps per scheduler a single dependent chain of 128 would be latency-bound.
+        float mx[4] = {x[0], x[1], x[2], x[3]};
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+          mx[0] = fmaxf(mx[0], x[c + 0]);
+          mx[1] = fmaxf(mx[1], x[c + 1]);
+          mx[2] = fmaxf(mx[2], x[c + 2]);
+          mx[3] = fmaxf(mx[3], x[c + 3]);
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        // running maximum (see kLazyTau)
+        const float m_new = (mt > m_run + kLazyTau) ? mt : m_run;
+        const float neg = -m_new * kLog2e;
+        const float alpha = ex2(fmaf(m_run, kLog2e, neg));
+        m_run = m_new;
+
+        if (kt > 0) {
+          // PV of the previous key tile must be done before O is rescaled and P reused.
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (g - 1) & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t acc[32];
+              tmem_ld32(tO + 32 * c, acc);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+              tmem_st32(tO + 32 * c, acc);
+            }
+          }
+        }
+        // The two slots take turns in the exp phase, so that one slot's loads, bias
+        // FMAs and maximum overlap the other's exponentials instead of both phases
+        // running in lockstep.  Slot 0 goes first; each slot passes the turn on
+        // after issuing its exponentials.
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bar(TOKEN + r), (r == 0) ? ((g & 1) ^ 1) : (g & 1), abort_flag));
+        if (!ok) break;
+        // exp and P store in chunks of 32 keys, so a packed chunk leaves the
+        // registers as soon as it is made; four independent partial sums.
+        float sm[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const int c = ch * 32 + e;
+            const float p0 = ex2(fmaf(x[c + 0], kLog2e, neg));
+            const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
+            const float p2 = ex2(fmaf(x[c + 2], kLog2e, neg));
+            const float p3 = ex2(fmaf(x[c + 3], kLog2e, neg));
+            sm[0] += p0;
+            sm[1] += p1;
+            sm[2] += p2;
+            sm[3] += p3;
+            pk[(e >> 1) + 0] = pack2<T>(p0, p1);
+            pk[(e >> 1) + 1] = pack2<T>(p2, p3);
+          }
+          tmem_st16(tP + ch * 16, pk);
+        }
+        l_run = fmaf(l_run, alpha, (sm[0] + sm[1]) + (sm[2] + sm[3]));
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(TOKEN + (r ^ 1)));
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + r));
       }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_READY + r));
-    }
-    };
-    if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
+      };
+      if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
+      if (!ok) break;
 
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (nkt - 1) & 1, abort_flag));
-    if (ok) {
+      // epilogue of the item: O / l and lse
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (g - 1) & 1, abort_flag));
+      if (!ok) break;
       tc_fence_after();
       const int j = jt * kBJ + t;
       const float inv = 1.f / l_run;
       T* dst = reinterpret_cast<T*>(o.p) + b * o.sb + h * o.sh + (int64_t)i * o.si + (int64_t)j * o.sj;
+      uint32_t acc[D];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(tO + 32 * c, acc);
-        tmem_wait_ld();
-        if (j < n) {
+      for (int c = 0; c < D / 32; ++c) tmem_ld32(tO + 32 * c, acc + 32 * c);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(O_FREE + r));  // the next item's first PV may overwrite O
+      if (do_store && j < n) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 u;
-            u.x = pack2<T>(__uint_as_float(acc[e + 0]) * inv, __uint_as_float(acc[e + 1]) * inv);
-            u.y = pack2<T>(__uint_as_float(acc[e + 2]) * inv, __uint_as_float(acc[e + 3]) * inv);
-            u.z = pack2<T>(__uint_as_float(acc[e + 4]) * inv, __uint_as_float(acc[e + 5]) * inv);
-            u.w = pack2<T>(__uint_as_float(acc[e + 6]) * inv, __uint_as_float(acc[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + 32 * c + e) = u;
-          }
+        for (int e = 0; e < D; e += 8) {
+          uint4 u;
+          u.x = pack2<T>(__uint_as_float(acc[e + 0]) * inv, __uint_as_float(acc[e + 1]) * inv);
+          u.y = pack2<T>(__uint_as_float(acc[e + 2]) * inv, __uint_as_float(acc[e + 3]) * inv);
+          u.z = pack2<T>(__uint_as_float(acc[e + 4]) * inv, __uint_as_float(acc[e + 5]) * inv);
+          u.w = pack2<T>(__uint_as_float(acc[e + 6]) * inv, __uint_as_float(acc[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + e) = u;
         }
-      }
-      if (j < n)
         lse[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + j] =
             row_full ? dm.sentinel : fmaf(lg2(l_run), kLn2, m_run);
+      }
     }
   }
   }
@@ -454,6 +504,19 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+int sm_count() {
+  static int count[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (count[dev] == 0) {
+    int c = 0;
+    cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev);
+    count[dev] = c > 0 ? c : 148;
+  }
+  return count[dev];
 }
 
 template <typename T, int D, int R, int NS>
@@ -484,8 +547,13 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
   auto kern = tc_fwd_kernel<T, D, R, NS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((dm.n + kBJ - 1) / kBJ, (dm.n_rows + R - 1) / R, dm.batch * dm.heads);
-  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, dm, a.status);
+  ItemGrid items;
+  items.njt = (dm.n + kBJ - 1) / kBJ;
+  items.nrp = (dm.n_rows + R - 1) / R;
+  items.total = items.njt * items.nrp * dm.batch * dm.heads;
+  const int grid = items.total < sm_count() ? items.total : sm_count();
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, dm, items,
+                                              a.status);
   return cudaGetLastError();
 }
 
@@ -555,6 +623,8 @@ bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
     if ((a->bias.sj * 2) % 16 || (a->bias.sh * 2) % 16 || (a->bias.sb * 2) % 16) return false;
     if (((uintptr_t)a->bias.p) & 15) return false;
     if (((uintptr_t)a->o.p) & 15 || (a->o.sj * 2) % 16) return false;
+    // the key mask is read four bytes at a time
+    if (((uintptr_t)a->mask.p) & 3 || a->mask.sb % 4 || a->mask.si % 4) return false;
   }
   return tc::get_encode_tiled() != nullptr;
 }
