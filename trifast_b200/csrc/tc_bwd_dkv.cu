@@ -1,7 +1,8 @@
 // dk and dv of triangle attention on the tensor cores (bf16 / fp16).
 //
-// One CTA owns a 128-key tile of R consecutive pair rows ("slots") and walks the
-// queries in tiles of 64.  Everything is computed transposed, keys on the TMEM
+// A work item is a 128-key tile of R consecutive pair rows ("slots"), walked over
+// the queries in tiles of 64; CTAs are persistent (one per SM, looping over items)
+// so the loads of the next item overlap the tail of the current one.  Everything is computed transposed, keys on the TMEM
 // lanes, so that P^T and dS^T feed the second pair of MMAs straight from TMEM:
 //     S^T  = K Q^T            (SS MMA, 128 keys x 64 queries)
 //     dP^T = V dO^T           (SS MMA)
@@ -58,16 +59,22 @@ struct DkvCfg {
   static int smem_bytes() { return 1024 + 1024 + kTilesBytes; }
 };
 
+struct ItemGrid {
+  int nkt, nrp, total;
+};
+
 template <typename T, int D, int R, int NS>
 __global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
               const __grid_constant__ CUtensorMap map_bt, const __grid_constant__ CUtensorMap map_lse,
               const __grid_constant__ CUtensorMap map_delta, View5 dk, View5 dv,
-              const uint8_t* __restrict__ rowfull, MaskView mask, Dims dm, unsigned int* status) {
+              const uint8_t* __restrict__ rowfull, MaskView mask, Dims dm, ItemGrid items,
+              unsigned int* status) {
   using Cfg = DkvCfg<D, R, NS>;
-  constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                P_READY = S_FREE + R, ACC_DONE = P_READY + R, NBARS = ACC_DONE + R;
+  constexpr int IN_FULL = 0, IN_EMPTY = 1, FULL = 2, EMPTY = FULL + NS, S_FULL = EMPTY + NS,
+                S_FREE = S_FULL + R, P_READY = S_FREE + R, ACC_DONE = P_READY + R,
+                ACC_FREE = ACC_DONE + R, NBARS = ACC_FREE + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
   constexpr int kSlot = Cfg::kSlotCols;
 
@@ -98,25 +105,40 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   auto delta_off = [&](int s, int r) -> uint32_t {
     return bias_off(s) + Cfg::kBiasBytes + (R + r) * Cfg::kVecBytes;
   };
+  // item -> (key tile, first row, head, batch); a slot beyond the last row re-does the
+  // last row (its loads stay in range, its results are not stored)
+  struct Item {
+    int kt, i0, h, b;
+  };
+  auto decode = [&](int w) -> Item {
+    Item it;
+    it.kt = w % items.nkt;
+    const int rest = w / items.nkt;
+    it.i0 = (rest % items.nrp) * R;
+    const int bh = rest / items.nrp;
+    it.h = bh % dm.heads;
+    it.b = bh / dm.heads;
+    return it;
+  };
+  auto slot_row = [&](const Item& it, int r) -> int { return min(it.i0 + r, dm.n_rows - 1); };
 
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
-  const int b = bh / dm.heads, h = bh % dm.heads;
-  const int nslots = min(R, dm.n_rows - i0);
 
   if (tid == 0) {
-    mbar_init(bar(kInFull), 1);
+    mbar_init(bar(IN_FULL), 1);
+    mbar_init(bar(IN_EMPTY), R);
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar(FULL + s), 1);
-      mbar_init(bar(EMPTY + s), nslots * 5);
+      mbar_init(bar(EMPTY + s), R * 5);
     }
     for (int r = 0; r < R; ++r) {
       mbar_init(bar(S_FULL + r), 1);
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(P_READY + r), 4);
       mbar_init(bar(ACC_DONE + r), 1);
+      mbar_init(bar(ACC_FREE + r), 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -144,34 +166,42 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     if (warp == 4 * R) {
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar(kInFull), nslots * 2 * Cfg::kKVBytes);
-        for (int r = 0; r < nslots; ++r) {
-          tma_load_5d(k_tile(r), &map_k, bar(kInFull), 0, kt * kBKeys, i0 + r, h, b);
-          tma_load_5d(v_tile(r), &map_v, bar(kInFull), 0, kt * kBKeys, i0 + r, h, b);
-        }
-        for (int jt = 0; jt < njt; ++jt) {
-          const int s = jt % NS;
-          if (jt >= NS && !mbar_wait(bar(EMPTY + s), ((jt / NS) - 1) & 1, abort_flag)) break;
-          mbar_arrive_expect_tx(bar(FULL + s),
-                                nslots * (2 * Cfg::kQBytes + 2 * Cfg::kVecBytes) + Cfg::kBiasBytes);
-          for (int r = 0; r < nslots; ++r) {
-            tma_load_5d(q_tile(s, r), &map_q, bar(FULL + s), 0, jt * kBJ, i0 + r, h, b);
-            tma_load_5d(do_tile(s, r), &map_do, bar(FULL + s), 0, jt * kBJ, i0 + r, h, b);
-            tma_load_4d(base + lse_off(s, r), &map_lse, bar(FULL + s), jt * kBJ, i0 + r, h, b);
-            tma_load_4d(base + delta_off(s, r), &map_delta, bar(FULL + s), jt * kBJ, i0 + r, h, b);
+        int g = 0, it = 0;  // running query-tile and item counters (barrier phases)
+        bool ok = true;
+        for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+          const Item im = decode(w);
+          if (it > 0) ok = mbar_wait(bar(IN_EMPTY), (it - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(IN_FULL), R * 2 * Cfg::kKVBytes);
+          for (int r = 0; r < R; ++r) {
+            tma_load_5d(k_tile(r), &map_k, bar(IN_FULL), 0, im.kt * kBKeys, slot_row(im, r), im.h, im.b);
+            tma_load_5d(v_tile(r), &map_v, bar(IN_FULL), 0, im.kt * kBKeys, slot_row(im, r), im.h, im.b);
           }
-          tma_load_4d(base + bias_off(s), &map_bt, bar(FULL + s), jt * kBJ, kt * kBKeys, h, b);
+          for (int jt = 0; jt < njt; ++jt, ++g) {
+            const int s = g % NS;
+            if (g >= NS) ok = mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar(FULL + s),
+                                  R * (2 * Cfg::kQBytes + 2 * Cfg::kVecBytes) + Cfg::kBiasBytes);
+            for (int r = 0; r < R; ++r) {
+              const int i = slot_row(im, r);
+              tma_load_5d(q_tile(s, r), &map_q, bar(FULL + s), 0, jt * kBJ, i, im.h, im.b);
+              tma_load_5d(do_tile(s, r), &map_do, bar(FULL + s), 0, jt * kBJ, i, im.h, im.b);
+              tma_load_4d(base + lse_off(s, r), &map_lse, bar(FULL + s), jt * kBJ, i, im.h, im.b);
+              tma_load_4d(base + delta_off(s, r), &map_delta, bar(FULL + s), jt * kBJ, i, im.h, im.b);
+            }
+            tma_load_4d(base + bias_off(s), &map_bt, bar(FULL + s), jt * kBJ, im.kt * kBKeys, im.h, im.b);
+          }
         }
       }
-    } else if (warp - (4 * R + 1) < nslots) {
+    } else if (warp - (4 * R + 1) < R) {
       // ---------------------------------------------------------- MMA issuers (one per slot)
       const int r = warp - (4 * R + 1);
       if (lane == 0) {
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc_s = make_idesc(128, kBJ, kBf16, false, false);
         constexpr uint32_t idesc_acc = make_idesc(128, D, kBf16, false, true);
-        auto issue_s_dp = [&](int r_, int s) {
-          const int r = r_;
+        auto issue_s_dp = [&](int s) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t ak = make_smem_desc(k_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -186,93 +216,108 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           }
           umma_commit(bar(S_FULL + r));
         };
-        bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_s_dp(r, 0);
-        }
-        for (int jt = 0; jt < njt && ok; ++jt) {
-          const int s = jt % NS;
-          if (jt + 1 < njt) {
-            const int ns = (jt + 1) % NS;
-            ok = mbar_wait(bar(FULL + ns), ((jt + 1) / NS) & 1, abort_flag) &&
-                 mbar_wait(bar(S_FREE + r), jt & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_s_dp(r, ns);
-          }
-          ok = mbar_wait(bar(P_READY + r), jt & 1, abort_flag);
+        int g = 0, it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+          ok = mbar_wait(bar(IN_FULL), it & 1, abort_flag) &&
+               mbar_wait(bar(FULL + g % NS), (g / NS) & 1, abort_flag) &&
+               (g == 0 || mbar_wait(bar(S_FREE + r), (g - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after();
-          const uint32_t acc = (jt > 0) ? 1u : 0u;
+          issue_s_dp(g % NS);
+          if (njt == 1) umma_commit(bar(IN_EMPTY));
+          for (int jt = 0; jt < njt && ok; ++jt, ++g) {
+            const int s = g % NS;
+            if (jt + 1 < njt) {
+              const int ns = (g + 1) % NS;
+              ok = mbar_wait(bar(FULL + ns), ((g + 1) / NS) & 1, abort_flag) &&
+                   mbar_wait(bar(S_FREE + r), g & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s_dp(ns);
+              if (jt + 2 == njt) umma_commit(bar(IN_EMPTY));  // last read of this item's K, V
+            }
+            ok = mbar_wait(bar(P_READY + r), g & 1, abort_flag);
+            // the first accumulating MMAs of an item overwrite dK, dV: the previous
+            // epilogue must have read them
+            if (ok && jt == 0 && it > 0) ok = mbar_wait(bar(ACC_FREE + r), (it - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = (jt > 0) ? 1u : 0u;
 #pragma unroll
-          for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO
-            const uint64_t bd = make_smem_desc(do_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                               Cfg::kSbo, Cfg::kSwz);
-            umma_ts(tmem_base + r * kSlot + 192 + D, tmem_base + r * kSlot + 128 + ks * 8, bd,
-                    idesc_acc, (ks > 0) ? 1u : acc);
-          }
+            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO
+              const uint64_t bd = make_smem_desc(do_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * kSlot + 192 + D, tmem_base + r * kSlot + 128 + ks * 8, bd,
+                      idesc_acc, (ks > 0) ? 1u : acc);
+            }
 #pragma unroll
-          for (int ks = 0; ks < kBJ / 16; ++ks) {  // dK += dS^T Q
-            const uint64_t bd = make_smem_desc(q_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                               Cfg::kSbo, Cfg::kSwz);
-            umma_ts(tmem_base + r * kSlot + 192, tmem_base + r * kSlot + 160 + ks * 8, bd,
-                    idesc_acc, (ks > 0) ? 1u : acc);
+            for (int ks = 0; ks < kBJ / 16; ++ks) {  // dK += dS^T Q
+              const uint64_t bd = make_smem_desc(q_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * kSlot + 192, tmem_base + r * kSlot + 160 + ks * 8, bd,
+                      idesc_acc, (ks > 0) ? 1u : acc);
+            }
+            umma_commit(bar(ACC_DONE + r));
+            umma_commit(bar(EMPTY + s));
           }
-          umma_commit(bar(ACC_DONE + r));
-          umma_commit(bar(EMPTY + s));
         }
       }
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
-    if (warp / 4 < nslots) {
-      // ---------------------------------------------------------- elementwise warpgroup
+    {
+      // ---------------------------------------------------------- elementwise warpgroups
       const int r = warp / 4, wq = warp & 3, t = tid & 127;
-      const int i = i0 + r;
-      const int key = kt * kBKeys + t;
       const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
       const uint32_t tS = tmem_base + lane_base + r * kSlot;
       const uint32_t tDP = tS + 64, tP = tS + 128, tDS = tS + 160, tDK = tS + 192, tDV = tS + 192 + D;
-      const bool row_full = rowfull[b * dm.n_rows + i] != 0;
-      // weight of this thread's key: 0 when dropped (or beyond n); on a fully masked
-      // row every key inside n weighs 1/n
-      const bool dropped =
-          key >= n || (!row_full && mask.p[b * mask.sb + (int64_t)i * mask.si + key] != 0);
       const float c1 = dm.scale * kLog2e;
       const float uniform = 1.f / (float)n;
 
+      int g = 0, it = 0;
       bool ok = true;
-      // The key weight pattern is fixed for the whole query loop, so the loop is
-      // instantiated per pattern of this warp: 0 = every key kept (no selects),
-      // 1 = mixed, 2 = every key dropped (no exponentials), 3 = fully masked row.
-      const int mode = row_full ? 3
-                       : __all_sync(0xffffffffu, !dropped) ? 0
-                       : __all_sync(0xffffffffu, dropped)  ? 2
-                                                           : 1;
-      auto query_loop = [&](auto mode_tag) {
-      constexpr int kMode = decltype(mode_tag)::value;
-      for (int jt = 0; jt < njt; ++jt) {
-        const int s = jt % NS;
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), jt & 1, abort_flag));
-        if (!ok) break;
-        tc_fence_after();
-        float x[64], g[64];
-        {
-          uint32_t* xr = reinterpret_cast<uint32_t*>(x);
-          uint32_t* gr = reinterpret_cast<uint32_t*>(g);
-          tmem_ld32(tS + 0, xr + 0);
-          tmem_ld32(tS + 32, xr + 32);
-          tmem_ld32(tDP + 0, gr + 0);
-          tmem_ld32(tDP + 32, gr + 32);
-          tmem_wait_ld();
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(S_FREE + r));
+      for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+        const Item im = decode(w);
+        const int i = slot_row(im, r);
+        const bool do_store = im.i0 + r < dm.n_rows;
+        const int b = im.b, h = im.h;
+        const int key = im.kt * kBKeys + t;
+        const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+        // weight of this thread's key: 0 when dropped (or beyond n); on a fully masked
+        // row every key inside n weighs 1/n
+        const bool dropped =
+            key >= n || (!row_full && mask.p[b * mask.sb + (int64_t)i * mask.si + key] != 0);
+        // The key weight pattern is fixed for the whole query loop, so the loop is
+        // instantiated per pattern of this warp: 0 = every key kept (no selects),
+        // 1 = mixed, 2 = every key dropped (no exponentials), 3 = fully masked row.
+        const int mode = row_full ? 3
+                         : __all_sync(0xffffffffu, !dropped) ? 0
+                         : __all_sync(0xffffffffu, dropped)  ? 2
+                                                             : 1;
+        auto query_loop = [&](auto mode_tag) {
+        constexpr int kMode = decltype(mode_tag)::value;
+        for (int jt = 0; jt < njt; ++jt, ++g) {
+          const int s = g % NS;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          float x[64], g_[64];
+          {
+            uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+            uint32_t* gr = reinterpret_cast<uint32_t*>(g_);
+            tmem_ld32(tS + 0, xr + 0);
+            tmem_ld32(tS + 32, xr + 32);
+            tmem_ld32(tDP + 0, gr + 0);
+            tmem_ld32(tDP + 32, gr + 32);
+            tmem_wait_ld();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(S_FREE + r));
 
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (jt / NS) & 1, abort_flag));
-        if (!ok) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
+          if (!ok) break;
         // One fused pass per 8 queries: bias^T / lse / delta loads, unpack, FMAs, the
         // exponential, dS and both 16-bit packs, so that the LSU, ALU, FMA and MUFU
         // pipes overlap inside one warp.
@@ -309,7 +354,7 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             for (int e = 0; e < 8; e += 2) {
               const int c = q8 * 8 + e;
               uint32_t wp = pack2<T>(p[e], p[e + 1]);
-              uint32_t wd = pack2<T>(p[e] * (g[c] - dl[e]), p[e + 1] * (g[c + 1] - dl[e + 1]));
+              uint32_t wd = pack2<T>(p[e] * (g_[c] - dl[e]), p[e + 1] * (g_[c + 1] - dl[e + 1]));
               if (kMode == 1 || kMode == 3) {  // dropped keys weigh exactly zero
                 wp = dropped ? 0u : wp;
                 wd = dropped ? 0u : wd;
@@ -320,62 +365,59 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias^T, lse, delta consumed by this warp
+          if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias^T, lse, delta consumed by this warp
 
-        if (jt > 0) {  // the accumulating MMAs of the previous query tile still read P^T, dS^T
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (jt - 1) & 1, abort_flag));
-          if (!ok) break;
+          if (jt > 0) {  // the accumulating MMAs of the previous query tile still read P^T, dS^T
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (g - 1) & 1, abort_flag));
+            if (!ok) break;
+          }
+          tmem_st32(tP, pp);
+          tmem_st32(tDS, pd);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(P_READY + r));
         }
-        tmem_st32(tP, pp);
-        tmem_st32(tDS, pd);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(P_READY + r));
-      }
-      };
-      switch (mode) {
-        case 0: query_loop(std::integral_constant<int, 0>{}); break;
-        case 1: query_loop(std::integral_constant<int, 1>{}); break;
-        case 2: query_loop(std::integral_constant<int, 2>{}); break;
-        default: query_loop(std::integral_constant<int, 3>{}); break;
-      }
+        };
+        switch (mode) {
+          case 0: query_loop(std::integral_constant<int, 0>{}); break;
+          case 1: query_loop(std::integral_constant<int, 1>{}); break;
+          case 2: query_loop(std::integral_constant<int, 2>{}); break;
+          default: query_loop(std::integral_constant<int, 3>{}); break;
+        }
+        if (!ok) break;
 
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (njt - 1) & 1, abort_flag));
-      if (ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_DONE + r), (g - 1) & 1, abort_flag));
+        if (!ok) break;
         tc_fence_after();
-        T* dst_k = reinterpret_cast<T*>(dk.p) + b * dk.sb + h * dk.sh + (int64_t)i * dk.si +
-                   (int64_t)key * dk.sj;
-        T* dst_v = reinterpret_cast<T*>(dv.p) + b * dv.sb + h * dv.sh + (int64_t)i * dv.si +
-                   (int64_t)key * dv.sj;
+        uint32_t acck[D], accv[D];
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t acc[32];
-          tmem_ld32(tDK + 32 * c, acc);
-          tmem_wait_ld();
-          if (key < n) {
+          tmem_ld32(tDK + 32 * c, acck + 32 * c);
+          tmem_ld32(tDV + 32 * c, accv + 32 * c);
+        }
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(ACC_FREE + r));  // the next item may overwrite dK, dV
+        if (do_store && key < n) {
+          T* dst_k = reinterpret_cast<T*>(dk.p) + b * dk.sb + h * dk.sh + (int64_t)i * dk.si +
+                     (int64_t)key * dk.sj;
+          T* dst_v = reinterpret_cast<T*>(dv.p) + b * dv.sb + h * dv.sh + (int64_t)i * dv.si +
+                     (int64_t)key * dv.sj;
 #pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(acc[e + 0]) * dm.scale, __uint_as_float(acc[e + 1]) * dm.scale);
-              u.y = pack2<T>(__uint_as_float(acc[e + 2]) * dm.scale, __uint_as_float(acc[e + 3]) * dm.scale);
-              u.z = pack2<T>(__uint_as_float(acc[e + 4]) * dm.scale, __uint_as_float(acc[e + 5]) * dm.scale);
-              u.w = pack2<T>(__uint_as_float(acc[e + 6]) * dm.scale, __uint_as_float(acc[e + 7]) * dm.scale);
-              *reinterpret_cast<uint4*>(dst_k + 32 * c + e) = u;
-            }
-          }
-          tmem_ld32(tDV + 32 * c, acc);
-          tmem_wait_ld();
-          if (key < n) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(acc[e + 0]), __uint_as_float(acc[e + 1]));
-              u.y = pack2<T>(__uint_as_float(acc[e + 2]), __uint_as_float(acc[e + 3]));
-              u.z = pack2<T>(__uint_as_float(acc[e + 4]), __uint_as_float(acc[e + 5]));
-              u.w = pack2<T>(__uint_as_float(acc[e + 6]), __uint_as_float(acc[e + 7]));
-              *reinterpret_cast<uint4*>(dst_v + 32 * c + e) = u;
-            }
+          for (int e = 0; e < D; e += 8) {
+            uint4 u;
+            u.x = pack2<T>(__uint_as_float(acck[e + 0]) * dm.scale, __uint_as_float(acck[e + 1]) * dm.scale);
+            u.y = pack2<T>(__uint_as_float(acck[e + 2]) * dm.scale, __uint_as_float(acck[e + 3]) * dm.scale);
+            u.z = pack2<T>(__uint_as_float(acck[e + 4]) * dm.scale, __uint_as_float(acck[e + 5]) * dm.scale);
+            u.w = pack2<T>(__uint_as_float(acck[e + 6]) * dm.scale, __uint_as_float(acck[e + 7]) * dm.scale);
+            *reinterpret_cast<uint4*>(dst_k + e) = u;
+            u.x = pack2<T>(__uint_as_float(accv[e + 0]), __uint_as_float(accv[e + 1]));
+            u.y = pack2<T>(__uint_as_float(accv[e + 2]), __uint_as_float(accv[e + 3]));
+            u.z = pack2<T>(__uint_as_float(accv[e + 4]), __uint_as_float(accv[e + 5]));
+            u.w = pack2<T>(__uint_as_float(accv[e + 6]), __uint_as_float(accv[e + 7]));
+            *reinterpret_cast<uint4*>(dst_v + e) = u;
           }
         }
       }
@@ -439,9 +481,17 @@ cudaError_t launch_dkv(const BwdArgs& a, cudaStream_t stream) {
   auto kern = tc_dkv_kernel<T, D, R, NS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((dm.n + kBKeys - 1) / kBKeys, (dm.n_rows + R - 1) / R, dm.batch * dm.heads);
+  ItemGrid items;
+  items.nkt = (dm.n + kBKeys - 1) / kBKeys;
+  items.nrp = (dm.n_rows + R - 1) / R;
+  items.total = items.nkt * items.nrp * dm.batch * dm.heads;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const int grid = items.total < sms ? items.total : sms;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dk, a.dv,
-                                              a.rowfull, a.mask, dm, a.status);
+                                              a.rowfull, a.mask, dm, items, a.status);
   return cudaGetLastError();
 }
 

@@ -1,8 +1,9 @@
 // dq of triangle attention on the tensor cores (bf16 / fp16).
 //
-// Same decomposition as the forward: one CTA owns a 128-query tile of two
-// consecutive pair rows ("slots", sharing the bias tiles) and walks the keys, in
-// tiles of 64.  Per slot and key tile:
+// Same decomposition as the forward: a work item is a 128-query tile of two
+// consecutive pair rows ("slots", sharing the bias tiles) walked over the keys in
+// tiles of 64; CTAs are persistent (one per SM, looping over items) so the loads of
+// the next item overlap the tail of the current one.  Per slot and key tile:
 //     S  = Q K^T          (SS MMA, 128 x 64)      dP = dO V^T        (SS MMA, 128 x 64)
 //     P  = exp2(S * c + bias * log2e - lse * log2e)   (recomputed from the saved lse)
 //     dS = P * (dP - delta)  -> 16-bit -> TMEM
@@ -54,9 +55,13 @@ struct DqCfg {
   static constexpr int kSbo = 8 * kRowBytes;
   static int mask_words(int n) { return ((n + 127) / 128) * 4; }
   static int smem_bytes(int n) {
-    const int head = (kHeaderBytes + R * mask_words(n) * 4 + 1023) / 1024 * 1024;
+    const int head = (kHeaderBytes + 4 * R * mask_words(n) * 4 + 1023) / 1024 * 1024;
     return 1024 + head + kTilesBytes;
   }
+};
+
+struct ItemGrid {
+  int njt, nrp, total;
 };
 
 template <typename T, int D, int NS>
@@ -65,11 +70,12 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_b, View5 dq, const float* __restrict__ lse,
              const float* __restrict__ delta, const uint8_t* __restrict__ rowfull, MaskView mask,
-             Dims dm, unsigned int* status) {
+             Dims dm, ItemGrid items, unsigned int* status) {
   using Cfg = DqCfg<D, NS>;
   constexpr int R = Cfg::R;
-  constexpr int kInFull = 0, FULL = 1, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + R,
-                DS_READY = S_FREE + R, DQ_DONE = DS_READY + R, NBARS = DQ_DONE + R;
+  constexpr int IN_FULL = 0, IN_EMPTY = 1, FULL = 2, EMPTY = FULL + NS, S_FULL = EMPTY + NS,
+                S_FREE = S_FULL + R, DS_READY = S_FREE + R, DQ_DONE = DS_READY + R,
+                DQ_FREE = DQ_DONE + R, NBARS = DQ_FREE + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
 
   extern __shared__ uint8_t smem_raw[];
@@ -78,12 +84,12 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   uint8_t* gbase = smem_raw + (base - raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
-  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [R][mask_words]
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][mask_words]
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
   const int mwords = ((n + 127) / 128) * 4;
-  const uint32_t tiles_off = (kHeaderBytes + R * mwords * 4 + 1023u) & ~1023u;
+  const uint32_t tiles_off = (kHeaderBytes + 4 * R * mwords * 4 + 1023u) & ~1023u;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kQBytes; };
@@ -96,25 +102,40 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     return base + stage_off(s) + (R + r) * Cfg::kKBytes;
   };
   auto bias_off = [&](int s) -> uint32_t { return stage_off(s) + 2 * R * Cfg::kKBytes; };
+  // item -> (j tile, first row, head, batch); a slot beyond the last row re-does the
+  // last row (its loads stay in range, its results are not stored)
+  struct Item {
+    int jt, i0, h, b;
+  };
+  auto decode = [&](int w) -> Item {
+    Item it;
+    it.jt = w % items.njt;
+    const int rest = w / items.njt;
+    it.i0 = (rest % items.nrp) * R;
+    const int bh = rest / items.nrp;
+    it.h = bh % dm.heads;
+    it.b = bh / dm.heads;
+    return it;
+  };
+  auto slot_row = [&](const Item& it, int r) -> int { return min(it.i0 + r, dm.n_rows - 1); };
 
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int jt = blockIdx.x, i0 = blockIdx.y * R, bh = blockIdx.z;
-  const int b = bh / dm.heads, h = bh % dm.heads;
-  const int nslots = min(R, dm.n_rows - i0);
 
   if (tid == 0) {
-    mbar_init(bar(kInFull), 1);
+    mbar_init(bar(IN_FULL), 1);
+    mbar_init(bar(IN_EMPTY), R);
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar(FULL + s), 1);
-      mbar_init(bar(EMPTY + s), nslots * 5);
+      mbar_init(bar(EMPTY + s), R * 5);
     }
     for (int r = 0; r < R; ++r) {
       mbar_init(bar(S_FULL + r), 1);
       mbar_init(bar(S_FREE + r), 4);
       mbar_init(bar(DS_READY + r), 4);
       mbar_init(bar(DQ_DONE + r), 1);
+      mbar_init(bar(DQ_FREE + r), 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -140,31 +161,38 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     if (warp == 4 * R) {
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar(kInFull), nslots * 2 * Cfg::kQBytes);
-        for (int r = 0; r < nslots; ++r) {
-          tma_load_5d(q_tile(r), &map_q, bar(kInFull), 0, jt * kBJ, i0 + r, h, b);
-          tma_load_5d(do_tile(r), &map_do, bar(kInFull), 0, jt * kBJ, i0 + r, h, b);
-        }
-        for (int kt = 0; kt < nkt; ++kt) {
-          const int s = kt % NS;
-          if (kt >= NS && !mbar_wait(bar(EMPTY + s), ((kt / NS) - 1) & 1, abort_flag)) break;
-          mbar_arrive_expect_tx(bar(FULL + s), nslots * 2 * Cfg::kKBytes + Cfg::kBiasBytes);
-          for (int r = 0; r < nslots; ++r) {
-            tma_load_5d(k_tile(s, r), &map_k, bar(FULL + s), 0, kt * kBK, i0 + r, h, b);
-            tma_load_5d(v_tile(s, r), &map_v, bar(FULL + s), 0, kt * kBK, i0 + r, h, b);
+        int g = 0, it = 0;  // running key-tile and item counters (barrier phases)
+        bool ok = true;
+        for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+          const Item im = decode(w);
+          if (it > 0) ok = mbar_wait(bar(IN_EMPTY), (it - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(IN_FULL), R * 2 * Cfg::kQBytes);
+          for (int r = 0; r < R; ++r) {
+            tma_load_5d(q_tile(r), &map_q, bar(IN_FULL), 0, im.jt * kBJ, slot_row(im, r), im.h, im.b);
+            tma_load_5d(do_tile(r), &map_do, bar(IN_FULL), 0, im.jt * kBJ, slot_row(im, r), im.h, im.b);
           }
-          tma_load_4d(base + bias_off(s), &map_b, bar(FULL + s), kt * kBK, jt * kBJ, h, b);
+          for (int kt = 0; kt < nkt; ++kt, ++g) {
+            const int s = g % NS;
+            if (g >= NS) ok = mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar(FULL + s), R * 2 * Cfg::kKBytes + Cfg::kBiasBytes);
+            for (int r = 0; r < R; ++r) {
+              tma_load_5d(k_tile(s, r), &map_k, bar(FULL + s), 0, kt * kBK, slot_row(im, r), im.h, im.b);
+              tma_load_5d(v_tile(s, r), &map_v, bar(FULL + s), 0, kt * kBK, slot_row(im, r), im.h, im.b);
+            }
+            tma_load_4d(base + bias_off(s), &map_b, bar(FULL + s), kt * kBK, im.jt * kBJ, im.h, im.b);
+          }
         }
       }
-    } else if (warp - (4 * R + 1) < nslots) {
+    } else if (warp - (4 * R + 1) < R) {
       // ---------------------------------------------------------- MMA issuers (one per slot)
       const int r = warp - (4 * R + 1);
       if (lane == 0) {
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc_s = make_idesc(128, kBK, kBf16, false, false);
         constexpr uint32_t idesc_dq = make_idesc(128, D, kBf16, false, true);
-        auto issue_s_dp = [&](int r_, int s) {
-          const int r = r_;
+        auto issue_s_dp = [&](int s) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t aq = make_smem_desc(q_tile(r) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
@@ -179,161 +207,189 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
           umma_commit(bar(S_FULL + r));
         };
-        bool ok = mbar_wait(bar(kInFull), 0, abort_flag) && mbar_wait(bar(FULL), 0, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_s_dp(r, 0);
-        }
-        for (int kt = 0; kt < nkt && ok; ++kt) {
-          const int s = kt % NS;
-          if (kt + 1 < nkt) {
-            const int ns = (kt + 1) % NS;
-            ok = mbar_wait(bar(FULL + ns), ((kt + 1) / NS) & 1, abort_flag) &&
-                 mbar_wait(bar(S_FREE + r), kt & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_s_dp(r, ns);
-          }
-          ok = mbar_wait(bar(DS_READY + r), kt & 1, abort_flag);
+        int g = 0, it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+          ok = mbar_wait(bar(IN_FULL), it & 1, abort_flag) &&
+               mbar_wait(bar(FULL + g % NS), (g / NS) & 1, abort_flag) &&
+               (g == 0 || mbar_wait(bar(S_FREE + r), (g - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after();
+          issue_s_dp(g % NS);
+          if (nkt == 1) umma_commit(bar(IN_EMPTY));
+          for (int kt = 0; kt < nkt && ok; ++kt, ++g) {
+            const int s = g % NS;
+            if (kt + 1 < nkt) {
+              const int ns = (g + 1) % NS;
+              ok = mbar_wait(bar(FULL + ns), ((g + 1) / NS) & 1, abort_flag) &&
+                   mbar_wait(bar(S_FREE + r), g & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s_dp(ns);
+              if (kt + 2 == nkt) umma_commit(bar(IN_EMPTY));  // last read of this item's Q, dO
+            }
+            ok = mbar_wait(bar(DS_READY + r), g & 1, abort_flag);
+            // the first dQ MMA of an item overwrites dQ: the previous epilogue must have read it
+            if (ok && kt == 0 && it > 0) ok = mbar_wait(bar(DQ_FREE + r), (it - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < kBK / 16; ++ks) {
-            const uint64_t bd = make_smem_desc(k_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
-                                               Cfg::kSbo, Cfg::kSwz);
-            umma_ts(tmem_base + r * 256 + 160, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_dq,
-                    (kt > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < kBK / 16; ++ks) {
+              const uint64_t bd = make_smem_desc(k_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
+                                                 Cfg::kSbo, Cfg::kSwz);
+              umma_ts(tmem_base + r * 256 + 160, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_dq,
+                      (kt > 0 || ks > 0) ? 1u : 0u);
+            }
+            umma_commit(bar(DQ_DONE + r));
+            umma_commit(bar(EMPTY + s));
           }
-          umma_commit(bar(DQ_DONE + r));
-          umma_commit(bar(EMPTY + s));
         }
       }
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
-    if (warp / 4 < nslots) {
-      // ---------------------------------------------------------- elementwise warpgroup
+    {
+      // ---------------------------------------------------------- elementwise warpgroups
       const int r = warp / 4, wq = warp & 3, t = tid & 127;
-      const int i = i0 + r;
-      const int j = jt * kBJ + t;
       const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
       const uint32_t tS = tmem_base + lane_base + r * 256;
       const uint32_t tDP = tS + 64, tDS = tS + 128, tDQ = tS + 160;
-      uint32_t* mb = maskbits + r * mwords;
-      const bool row_full = rowfull[b * dm.n_rows + i] != 0;
-
-      {  // key mask of row i as bit words; bit set = key dropped (or beyond n)
-        const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
-        for (int c = 0; c < mwords / 4; ++c) {
-          const int key = c * 128 + t;
-          const int dropped = (key < n) ? (row_full ? 0 : (mrow[key] != 0)) : 1;
-          const uint32_t bits = __ballot_sync(0xffffffffu, dropped);
-          if (lane == 0) mb[c * 4 + wq] = bits;
-        }
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + r) : "memory");
-      }
-      const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + min(j, n - 1);
-      const float neg_lse2 = -lse[stat] * kLog2e;
-      const float my_delta = delta[stat];
+      uint32_t* mb = maskbits + warp * mwords;  // this warp's own copy: no cross-warp sync
       const float c1 = dm.scale * kLog2e;
       const float uniform = 1.f / (float)n;
 
+      int g = 0, it = 0;
       bool ok = true;
-      auto key_loop = [&](auto row_full_tag) {
-        constexpr bool kRowFull = decltype(row_full_tag)::value;
-        for (int kt = 0; kt < nkt; ++kt) {
-          const int s = kt % NS;
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), kt & 1, abort_flag));
-          if (!ok) break;
-          tc_fence_after();
-          float x[64], g[64];
-          {
-            uint32_t* xr = reinterpret_cast<uint32_t*>(x);
-            uint32_t* gr = reinterpret_cast<uint32_t*>(g);
-            tmem_ld32(tS + 0, xr + 0);
-            tmem_ld32(tS + 32, xr + 32);
-            tmem_ld32(tDP + 0, gr + 0);
-            tmem_ld32(tDP + 32, gr + 32);
-            tmem_wait_ld();
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(S_FREE + r));
+      for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+        const Item im = decode(w);
+        const int i = slot_row(im, r);
+        const bool do_store = im.i0 + r < dm.n_rows;
+        const int b = im.b, h = im.h;
+        const int j = im.jt * kBJ + t;
+        const bool row_full = rowfull[b * dm.n_rows + i] != 0;
 
-          const uint32_t mw0 = mb[kt * 2 + 0], mw1 = mb[kt * 2 + 1];
-          const bool clean = (mw0 | mw1) == 0u;
-
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (kt / NS) & 1, abort_flag));
-          if (!ok) break;
-          // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
-          // exponential (MUFU), dS and the 16-bit pack, so that the pipes overlap
-          // inside one warp instead of running as separate phases.
-          uint32_t pk[32];
-          const uint8_t* brow = gbase + bias_off(s) + t * 128;
+        // Key mask of row i as bit words (bit set = key dropped or beyond n; none
+        // dropped inside n on a fully masked row).  Lane l reads keys 4l .. 4l+3 of a
+        // 128-key chunk as one word; word jb of the chunk holds, at bit l, key 4l + jb.
+        {
+          const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+          for (int c = 0; c < mwords / 4; ++c) {
+            const int key4 = c * 128 + 4 * lane;
+            uint32_t u = 0x01010101u;
+            if (key4 < n) u = row_full ? 0u : __ldg(reinterpret_cast<const uint32_t*>(mrow + key4));
 #pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) {
-            float p[8];
-            if (kRowFull) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) p[e] = uniform;
-            } else {
-              const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
-              float bv[8];
-              unpack2<T>(u.x, bv[0], bv[1]);
-              unpack2<T>(u.y, bv[2], bv[3]);
-              unpack2<T>(u.z, bv[4], bv[5]);
-              unpack2<T>(u.w, bv[6], bv[7]);
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, neg_lse2)));
+            for (int jb = 0; jb < 4; ++jb) {
+              const uint32_t bits = __ballot_sync(0xffffffffu, ((u >> (8 * jb)) & 0xffu) != 0u);
+              if (lane == 0) mb[c * 4 + jb] = bits;
             }
-            if (!clean) {
-              const uint32_t w = (q8 < 4) ? mw0 : mw1;
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                if ((w >> ((q8 * 8 + e) & 31)) & 1u) p[e] = 0.f;
-            }
-#pragma unroll
-            for (int e = 0; e < 8; e += 2)
-              pk[(q8 * 8 + e) >> 1] = pack2<T>(p[e] * (g[q8 * 8 + e] - my_delta),
-                                               p[e + 1] * (g[q8 * 8 + e + 1] - my_delta));
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
-
-          if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (kt - 1) & 1, abort_flag));
-            if (!ok) break;
-          }
-          tmem_st32(tDS, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(DS_READY + r));
         }
-      };
-      if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
+        const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + min(j, n - 1);
+        const float neg_lse2 = -lse[stat] * kLog2e;
+        const float my_delta = delta[stat];
 
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (nkt - 1) & 1, abort_flag));
-      if (ok) {
-        tc_fence_after();
-        T* dst = reinterpret_cast<T*>(dq.p) + b * dq.sb + h * dq.sh + (int64_t)i * dq.si +
-                 (int64_t)j * dq.sj;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t acc[32];
-          tmem_ld32(tDQ + 32 * c, acc);
-          tmem_wait_ld();
-          if (j < n) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(acc[e + 0]) * dm.scale, __uint_as_float(acc[e + 1]) * dm.scale);
-              u.y = pack2<T>(__uint_as_float(acc[e + 2]) * dm.scale, __uint_as_float(acc[e + 3]) * dm.scale);
-              u.z = pack2<T>(__uint_as_float(acc[e + 4]) * dm.scale, __uint_as_float(acc[e + 5]) * dm.scale);
-              u.w = pack2<T>(__uint_as_float(acc[e + 6]) * dm.scale, __uint_as_float(acc[e + 7]) * dm.scale);
-              *reinterpret_cast<uint4*>(dst + 32 * c + e) = u;
+        auto key_loop = [&](auto row_full_tag) {
+          constexpr bool kRowFull = decltype(row_full_tag)::value;
+          for (int kt = 0; kt < nkt; ++kt, ++g) {
+            const int s = g % NS;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+            float x[64], gd[64];
+            {
+              uint32_t* xr = reinterpret_cast<uint32_t*>(x);
+              uint32_t* gr = reinterpret_cast<uint32_t*>(gd);
+              tmem_ld32(tS + 0, xr + 0);
+              tmem_ld32(tS + 32, xr + 32);
+              tmem_ld32(tDP + 0, gr + 0);
+              tmem_ld32(tDP + 32, gr + 32);
+              tmem_wait_ld();
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(S_FREE + r));
+
+            // mask words of this 64-key tile: the tile is half (kt & 1) of chunk kt >> 1;
+            // column c is position pos = (kt & 1) * 64 + c: bit (pos >> 2) of word (pos & 3)
+            uint32_t mw[4];
+#pragma unroll
+            for (int jb = 0; jb < 4; ++jb) mw[jb] = (mb[(kt >> 1) * 4 + jb] >> ((kt & 1) * 16)) & 0xffffu;
+            const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
+
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
+            if (!ok) break;
+            // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
+            // exponential (MUFU), dS and the 16-bit pack.
+            uint32_t pk[32];
+            const uint8_t* brow = gbase + bias_off(s) + t * 128;
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+              float p[8];
+              if (kRowFull) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) p[e] = uniform;
+              } else {
+                const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
+                float bv[8];
+                unpack2<T>(u.x, bv[0], bv[1]);
+                unpack2<T>(u.y, bv[2], bv[3]);
+                unpack2<T>(u.z, bv[4], bv[5]);
+                unpack2<T>(u.w, bv[6], bv[7]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, neg_lse2)));
+              }
+              if (!clean) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int c = q8 * 8 + e;
+                  if ((mw[c & 3] >> (c >> 2)) & 1u) p[e] = 0.f;
+                }
+              }
+#pragma unroll
+              for (int e = 0; e < 8; e += 2)
+                pk[(q8 * 8 + e) >> 1] = pack2<T>(p[e] * (gd[q8 * 8 + e] - my_delta),
+                                                 p[e + 1] * (gd[q8 * 8 + e + 1] - my_delta));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+
+            if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
+              ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));
+              if (!ok) break;
+            }
+            tmem_st32(tDS, pk);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(DS_READY + r));
+          }
+        };
+        if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
+        if (!ok) break;
+
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t acc[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(tDQ + 32 * c, acc + 32 * c);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(DQ_FREE + r));  // the next item's first dQ MMA may overwrite dQ
+        if (do_store && j < n) {
+          T* dst = reinterpret_cast<T*>(dq.p) + b * dq.sb + h * dq.sh + (int64_t)i * dq.si +
+                   (int64_t)j * dq.sj;
+#pragma unroll
+          for (int e = 0; e < D; e += 8) {
+            uint4 u;
+            u.x = pack2<T>(__uint_as_float(acc[e + 0]) * dm.scale, __uint_as_float(acc[e + 1]) * dm.scale);
+            u.y = pack2<T>(__uint_as_float(acc[e + 2]) * dm.scale, __uint_as_float(acc[e + 3]) * dm.scale);
+            u.z = pack2<T>(__uint_as_float(acc[e + 4]) * dm.scale, __uint_as_float(acc[e + 5]) * dm.scale);
+            u.w = pack2<T>(__uint_as_float(acc[e + 6]) * dm.scale, __uint_as_float(acc[e + 7]) * dm.scale);
+            *reinterpret_cast<uint4*>(dst + e) = u;
           }
         }
       }
@@ -354,6 +410,13 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+int sm_count_dq() {
+  int dev = 0, c = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev);
+  return c > 0 ? c : 148;
 }
 
 template <typename T, int D, int NS>
@@ -387,9 +450,14 @@ cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
   auto kern = tc_dq_kernel<T, D, NS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((dm.n + kBJ - 1) / kBJ, (dm.n_rows + 1) / 2, dm.batch * dm.heads);
+  ItemGrid items;
+  items.njt = (dm.n + kBJ - 1) / kBJ;
+  items.nrp = (dm.n_rows + 1) / 2;
+  items.total = items.njt * items.nrp * dm.batch * dm.heads;
+  const int sms = sm_count_dq();
+  const int grid = items.total < sms ? items.total : sms;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mbias, a.dq, a.lse, a.delta,
-                                              a.rowfull, a.mask, dm, a.status);
+                                              a.rowfull, a.mask, dm, items, a.status);
   return cudaGetLastError();
 }
 
@@ -404,6 +472,8 @@ bool tc_backward_supported(const BwdArgs& a) {
   if (smem > kSmemLimit) return false;
   if ((a.bias.sj * 2) % 16 || (a.bias.sh * 2) % 16 || (a.bias.sb * 2) % 16) return false;
   if (((uintptr_t)a.bias.p) & 15) return false;
+  // the key mask is read four bytes at a time
+  if (((uintptr_t)a.mask.p) & 3 || a.mask.sb % 4 || a.mask.si % 4) return false;
   return tc::get_encode_tiled() != nullptr;
 }
 
