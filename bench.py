@@ -396,9 +396,11 @@ def run_native(args, w):
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": step.launches * args.steps,
-            "frac_of_bf16_peak": {"measured_burst": total_flops / (ms * 1e-3) / 1e12 / peaks["burst"],
-                                  "measured_sustained": total_flops / (ms * 1e-3) / 1e12 / peaks["sustained"],
-                                  "nominal_2250": total_flops / (ms * 1e-3) / 1e12 / 2250.0},
+            # fraction of the N GPUs' combined dense bf16 tensor peak
+            "frac_of_bf16_peak": {
+                "measured_burst": total_flops / (ms * 1e-3) / 1e12 / (peaks["burst"] * world),
+                "measured_sustained": total_flops / (ms * 1e-3) / 1e12 / (peaks["sustained"] * world),
+                "nominal_2250": total_flops / (ms * 1e-3) / 1e12 / (2250.0 * world)},
         }
         if phases is not None:
             line["phases_ms"] = phases
