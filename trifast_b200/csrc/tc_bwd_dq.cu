@@ -32,6 +32,10 @@ namespace {
 using namespace tc;
 
 constexpr int kBJ = 128, kBK = 64;
+#ifndef TRIFAST_DQ_TOKEN
+#define TRIFAST_DQ_TOKEN 0
+#endif
+constexpr bool kSlotToken = TRIFAST_DQ_TOKEN != 0;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSmemLimit = 232448;
 constexpr int kHeaderBytes = 512;
@@ -75,7 +79,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   constexpr int R = Cfg::R;
   constexpr int IN_FULL = 0, IN_EMPTY = 1, FULL = 2, EMPTY = FULL + NS, S_FULL = EMPTY + NS,
                 S_FREE = S_FULL + R, DS_READY = S_FREE + R, DQ_DONE = DS_READY + R,
-                DQ_FREE = DQ_DONE + R, NBARS = DQ_FREE + R;
+                DQ_FREE = DQ_DONE + R, TOKEN = DQ_FREE + R, NBARS = TOKEN + R;
   static_assert(NBARS * 8 <= 256, "barrier area");
 
   extern __shared__ uint8_t smem_raw[];
@@ -136,6 +140,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       mbar_init(bar(DS_READY + r), 4);
       mbar_init(bar(DQ_DONE + r), 1);
       mbar_init(bar(DQ_FREE + r), 4);
+      mbar_init(bar(TOKEN + r), 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -319,6 +324,13 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
             ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
             if (!ok) break;
+            // The two slots take turns in the pass below (it is MUFU-bound), so that one
+            // slot's waits, TMEM loads and stores overlap the other's exponentials.
+            if (kSlotToken) {
+              ok = __all_sync(0xffffffffu,
+                              mbar_wait(bar(TOKEN + r), (r == 0) ? ((g & 1) ^ 1) : (g & 1), abort_flag));
+              if (!ok) break;
+            }
             // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
             // exponential (MUFU), dS and the 16-bit pack.
             uint32_t pk[32];
@@ -353,7 +365,10 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
                                                  p[e + 1] * (gd[q8 * 8 + e + 1] - my_delta));
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+            if (lane == 0) {
+              mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
+              if (kSlotToken) mbar_arrive(bar(TOKEN + (r ^ 1)));
+            }
 
             if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
               ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));

@@ -361,17 +361,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                                             (((gq & 7) ^ (t & 7)) << 4));
             float b0, b1;
             unpack2<T>(u.x, b0, b1);
-            x[gq * 8 + 0] = fmaf(x[gq * 8 + 0], dm.scale, b0);
-            x[gq * 8 + 1] = fmaf(x[gq * 8 + 1], dm.scale, b1);
+            ffma2(x[gq * 8 + 0], x[gq * 8 + 1], x[gq * 8 + 0], x[gq * 8 + 1], dm.scale, dm.scale, b0, b1);
             unpack2<T>(u.y, b0, b1);
-            x[gq * 8 + 2] = fmaf(x[gq * 8 + 2], dm.scale, b0);
-            x[gq * 8 + 3] = fmaf(x[gq * 8 + 3], dm.scale, b1);
+            ffma2(x[gq * 8 + 2], x[gq * 8 + 3], x[gq * 8 + 2], x[gq * 8 + 3], dm.scale, dm.scale, b0, b1);
             unpack2<T>(u.z, b0, b1);
-            x[gq * 8 + 4] = fmaf(x[gq * 8 + 4], dm.scale, b0);
-            x[gq * 8 + 5] = fmaf(x[gq * 8 + 5], dm.scale, b1);
+            ffma2(x[gq * 8 + 4], x[gq * 8 + 5], x[gq * 8 + 4], x[gq * 8 + 5], dm.scale, dm.scale, b0, b1);
             unpack2<T>(u.w, b0, b1);
-            x[gq * 8 + 6] = fmaf(x[gq * 8 + 6], dm.scale, b0);
-            x[gq * 8 + 7] = fmaf(x[gq * 8 + 7], dm.scale, b1);
+            ffma2(x[gq * 8 + 6], x[gq * 8 + 7], x[gq * 8 + 6], x[gq * 8 + 7], dm.scale, dm.scale, b0, b1);
           }
         }
         __syncwarp();
@@ -386,12 +382,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // warps per scheduler a single dependent chain of 128 would be latency-bound.
         float mx[4] = {x[0], x[1], x[2], x[3]};
 #pragma unroll
-        for (int c = 4; c < 128; c += 4) {
-          mx[0] = fmaxf(mx[0], x[c + 0]);
-          mx[1] = fmaxf(mx[1], x[c + 1]);
-          mx[2] = fmaxf(mx[2], x[c + 2]);
-          mx[3] = fmaxf(mx[3], x[c + 3]);
+        for (int c = 4; c < 124; c += 8) {  // 3-input max: two scores per instruction
+          mx[0] = fmax3(mx[0], x[c + 0], x[c + 1]);
+          mx[1] = fmax3(mx[1], x[c + 2], x[c + 3]);
+          mx[2] = fmax3(mx[2], x[c + 4], x[c + 5]);
+          mx[3] = fmax3(mx[3], x[c + 6], x[c + 7]);
         }
+        mx[0] = fmax3(mx[0], x[124], x[125]);
+        mx[1] = fmax3(mx[1], x[126], x[127]);
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         // running maximum (see kLazyTau)
         const float m_new = (mt > m_run + kLazyTau) ? mt : m_run;
@@ -432,14 +430,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
             const int c = ch * 32 + e;
-            const float p0 = ex2(fmaf(x[c + 0], kLog2e, neg));
-            const float p1 = ex2(fmaf(x[c + 1], kLog2e, neg));
-            const float p2 = ex2(fmaf(x[c + 2], kLog2e, neg));
-            const float p3 = ex2(fmaf(x[c + 3], kLog2e, neg));
-            sm[0] += p0;
-            sm[1] += p1;
-            sm[2] += p2;
-            sm[3] += p3;
+            float a0, a1, a2, a3;
+            ffma2(a0, a1, x[c + 0], x[c + 1], kLog2e, kLog2e, neg, neg);
+            ffma2(a2, a3, x[c + 2], x[c + 3], kLog2e, kLog2e, neg, neg);
+            const float p0 = ex2(a0), p1 = ex2(a1), p2 = ex2(a2), p3 = ex2(a3);
+            fadd2(sm[0], sm[1], sm[0], sm[1], p0, p1);
+            fadd2(sm[2], sm[3], sm[2], sm[3], p2, p3);
             pk[(e >> 1) + 0] = pack2<T>(p0, p1);
             pk[(e >> 1) + 1] = pack2<T>(p2, p3);
           }
