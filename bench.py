@@ -191,6 +191,8 @@ class DirectStep:
         self.o = torch.empty_like(q)
         self.lse = torch.empty((bs, h, rows, n), dtype=torch.float32, device=dev)
         self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype)
+        self.fws_bytes = self.lib.trifast_forward_workspace_bytes(C.byref(self.shape))
+        self.fws = torch.empty(self.fws_bytes, dtype=torch.uint8, device=dev) if self.fws_bytes else None
         if w.backward:
             self.dq, self.dk, self.dv = (torch.empty_like(q) for _ in range(3))
             self.db = torch.empty_like(b)
@@ -217,7 +219,8 @@ class DirectStep:
         a, B = self.a, C.byref
         rc = self.lib.trifast_forward(B(self.shape), B(a["q"]), B(a["k"]), B(a["v"]), B(self.ab),
                                       B(self.am), B(a["o"]), C.c_void_p(self.lse.data_ptr()),
-                                      self.stream)
+                                      C.c_void_p(self.fws.data_ptr() if self.fws is not None else None),
+                                      C.c_size_t(self.fws_bytes), self.stream)
         self._lib.check(rc, "trifast_forward")
 
     def backward_db(self):

@@ -118,20 +118,27 @@ const char* trifast_status_str(int status);
  * instead of benchmarking and an on-disk cache.  Pure host code. */
 int trifast_pick_plan(const trifast_shape* shape, trifast_plan* plan);
 
-/* Bytes of caller-provided workspace the backward needs (delta + db partials).
- * The forward needs none.  Returns 0 on an invalid shape. */
+/* Bytes of caller-provided workspace the backward needs (delta, packed masks, fp32
+ * db and its row-split partials, bias copies).  Returns 0 on an invalid shape. */
 size_t trifast_backward_workspace_bytes(const trifast_shape* shape);
+
+/* Bytes of workspace the forward needs: 0 except on the tensor-core path with
+ * n % 8 != 0, which reads the bias through a copy with a 16-byte row pitch and the
+ * key mask through packed words (both made inside trifast_forward). */
+size_t trifast_forward_workspace_bytes(const trifast_shape* shape);
 
 /* Forward: o = softmax_k(q.k^T * d^-0.5 + bias + mask) v and lse (natural log).
  * Stands in for _triangle_attention + the _fwd kernel of the reference
  * (src/trifast/torch.py:17-65, src/trifast/triton.py:14-132).
  * Rows whose keys are all masked get uniform weights 1/n over all n keys, as
  * the reference's PyTorch path does (src/trifast/equiv.py:42-69); their lse is
- * stored as finfo(dtype).min. */
+ * stored as finfo(dtype).min.  `workspace` holds at least
+ * trifast_forward_workspace_bytes() bytes (NULL is fine when that is 0). */
 int trifast_forward(const trifast_shape* shape,
                     const trifast_t5* q, const trifast_t5* k, const trifast_t5* v,
                     const trifast_t4* bias, const trifast_mask* mask,
-                    const trifast_t5* o, float* lse, void* stream);
+                    const trifast_t5* o, float* lse,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* Whole backward on one device: dq, dk, dv and db (db in the input dtype).
  * Stands in for triangle_attention_bwd and its three kernels

@@ -46,7 +46,8 @@ def test_version_and_status_strings():
     (256, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),
     (32, 4, 32, torch.float32, _lib.KERNEL_SIMT),     # fp32 always on CUDA cores
     (1024, 4, 32, torch.float32, _lib.KERNEL_SIMT),
-    (191, 4, 32, torch.bfloat16, _lib.KERNEL_SIMT),   # bias row pitch not 16-byte
+    (191, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),  # ragged n: padded bias copy in the workspace
+    (100, 4, 32, torch.bfloat16, _lib.KERNEL_SIMT),
     (64, 1, 64, torch.bfloat16, _lib.KERNEL_SIMT),    # below one tile
     (256, 4, 128, torch.bfloat16, _lib.KERNEL_SIMT),
     (256, 4, 16, torch.float16, _lib.KERNEL_SIMT),
@@ -59,8 +60,17 @@ def test_heuristic_table(n, h, d, dtype, kernel):
         assert (plan["block_j"], plan["block_k"]) == (128, 128)
 
 
+def test_forward_workspace_only_for_ragged_n_on_tensor_cores():
+    lib = _lib.load()
+    for n, want in ((1024, False), (1000, False), (1001, True), (191, True), (100, False)):
+        shp = _lib.make_shape(1, 4, n, n, 32, torch.bfloat16)
+        assert (lib.trifast_forward_workspace_bytes(C.byref(shp)) > 0) == want, n
+    shp = _lib.make_shape(1, 4, 1001, 1001, 32, torch.float32)
+    assert lib.trifast_forward_workspace_bytes(C.byref(shp)) == 0
+
+
 def test_heuristic_rejects_impossible_forced_kernel():
-    shp = _lib.make_shape(1, 4, 191, 191, 32, torch.bfloat16, _lib.KERNEL_TCGEN05)
+    shp = _lib.make_shape(1, 4, 100, 100, 32, torch.bfloat16, _lib.KERNEL_TCGEN05)
     plan = _lib.Plan()
     assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == -10
 
@@ -96,7 +106,7 @@ def test_forward_argument_validation_needs_no_device():
 
     def call(q=t, k=t, v=t, b=bias, m=mask, o=t, l=lse):
         return lib.trifast_forward(C.byref(shp), C.byref(q), C.byref(k), C.byref(v), C.byref(b),
-                                   C.byref(m), C.byref(o), l, None)
+                                   C.byref(m), C.byref(o), l, None, 0, None)
 
     assert call(q=_fake5(ptr=0)) == -1                       # NULL data
     assert call(k=_fake5(ptr=0x1008)) == -6                  # misaligned

@@ -89,7 +89,7 @@ def seeded(n, h, d, dtype, use_mask, bs, std, seed=1337):
 
 SHAPES = [(16, 1, 16), (32, 1, 32), (64, 1, 64), (16, 4, 128), (191, 4, 32)] + \
          [(n, 4, 32) for n in (17, 31, 33, 63, 65, 96, 100, 127, 128, 129, 136, 160, 199)] + \
-         [(128, 2, 64), (144, 2, 64), (256, 2, 32), (264, 1, 32)]
+         [(128, 2, 64), (144, 2, 64), (256, 2, 32), (264, 1, 32), (257, 2, 32), (333, 1, 64)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
@@ -126,7 +126,7 @@ def test_named_workloads(name):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n", [48, 256])
+@pytest.mark.parametrize("n", [48, 131, 256])
 def test_masked_keys_have_exactly_zero_weight(dtype, n):
     q, k, v, b, m, do = seeded(n, 2, 32, dtype, True, 1, 1.0, seed=5)
     m[0, 3] = True                                     # one fully masked row as well
@@ -146,11 +146,11 @@ def test_masked_keys_have_exactly_zero_weight(dtype, n):
     assert float((a[0][0, :, 3] - mean_v[:, None, :]).abs().max()) < tol
 
 
+@pytest.mark.parametrize("n", [136, 203])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_row_shards_match_whole_problem(dtype):
+def test_row_shards_match_whole_problem(dtype, n):
     """Rows are independent: running rows [r0, r1) alone gives the same o, dq, dk, dv,
     bit for bit, and the shard db partials add up to the whole db."""
-    n = 136
     q, k, v, b, m, do = seeded(n, 2, 32, dtype, True, 1, 1.0, seed=9)
     whole = run_kernel(q, k, v, b, m, do)
     db = 0

@@ -50,8 +50,9 @@ SIGNATURES = {
     "trifast_status_str": (C.c_char_p, [C.c_int]),
     "trifast_pick_plan": (C.c_int, [_P(Shape), _P(Plan)]),
     "trifast_backward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
+    "trifast_forward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
     "trifast_forward": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T4), _P(Mask), _P(T5),
-                                  C.c_void_p, C.c_void_p]),
+                                  C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "trifast_backward": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4), _P(Mask),
                                    _P(T5), C.c_void_p, _P(T5), _P(T5), _P(T5), _P(T4),
                                    C.c_void_p, C.c_size_t, C.c_void_p]),

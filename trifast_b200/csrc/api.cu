@@ -97,6 +97,7 @@ Dims make_dims(const trifast_shape* s) {
   dm.n = s->n;
   dm.n_rows = s->n_rows;
   dm.d = s->d;
+  dm.n_pad = (s->n + 7) / 8 * 8;
   dm.scale = 1.0f / sqrtf((float)s->d);
   dm.sentinel = dtype_sentinel(s->dtype);
   return dm;
@@ -106,15 +107,41 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Carve-up of the backward workspace.
 struct Workspace {
-  size_t delta_off, nlse_off, rowfull_off, maskbits_off, db_off, bias_t_off, partial_off, total;
+  size_t delta_off, nlse_off, rowfull_off, maskbits_off, db_off, bias_t_off, bias_pad_off,
+      partial_off, total;
   int mask_words;
-  bool has_bias_t;
+  bool has_bias_t, has_bias_pad;
 };
+
+// Forward workspace: only the tensor-core path with n % 8 != 0 needs one (a copy of
+// the bias with a 16-byte row pitch, the packed key masks and the row flags).
+struct FwdWorkspace {
+  size_t rowfull_off, maskbits_off, bias_pad_off, total;
+  int mask_words;
+};
+
+FwdWorkspace carve_fwd(const trifast_shape* s, const trifast_plan& plan) {
+  FwdWorkspace w{};
+  w.mask_words = ((s->n + 127) / 128) * 4;
+  if (plan.kernel != TRIFAST_KERNEL_TCGEN05 || s->n % 8 == 0) return w;
+  const size_t n_pad = (size_t)(s->n + 7) / 8 * 8;
+  size_t off = 0;
+  w.rowfull_off = off;
+  off = (off + (size_t)s->batch * s->n_rows + 255) / 256 * 256;
+  w.maskbits_off = off;
+  off = (off + (size_t)s->batch * s->n_rows * w.mask_words * sizeof(uint32_t) + 255) / 256 * 256;
+  w.bias_pad_off = off;
+  off = (off + (size_t)s->batch * s->heads * s->n * n_pad * 2 + 255) / 256 * 256;
+  w.total = off;
+  return w;
+}
 
 Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   Workspace w;
-  const size_t stat = (size_t)s->batch * s->heads * s->n_rows * s->n * sizeof(float);
+  const size_t n_pad = (size_t)(s->n + 7) / 8 * 8;  // row pitch of the vectors and bias copies
+  const size_t stat = (size_t)s->batch * s->heads * s->n_rows * n_pad * sizeof(float);
   const size_t dbb = (size_t)s->batch * s->heads * s->n * s->n * sizeof(float);
+  const size_t bias_copy = (size_t)s->batch * s->heads * s->n * n_pad * 2;
   size_t off = 0;
   w.delta_off = off;
   off = align_up(off + stat, 256);
@@ -124,13 +151,18 @@ Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   off = align_up(off + (size_t)s->batch * s->n_rows, 256);
   w.mask_words = ((s->n + 127) / 128) * 4;
   w.maskbits_off = off;
-  off = align_up(off + (size_t)s->batch * s->n_rows * w.mask_words * sizeof(uint32_t), 256);
+  // two layouts of the packed key masks, one after the other (see BwdArgs)
+  off = align_up(off + 2 * (size_t)s->batch * s->n_rows * w.mask_words * sizeof(uint32_t), 256);
   w.db_off = off;
   off = align_up(off + dbb, 256);
   // transposed bias copy for the tensor-core dk/dv kernel (16-bit dtypes only)
   w.has_bias_t = plan.kernel == TRIFAST_KERNEL_TCGEN05;
   w.bias_t_off = off;
-  if (w.has_bias_t) off = align_up(off + dbb / 2, 256);
+  if (w.has_bias_t) off = align_up(off + bias_copy, 256);
+  // bias copy with a 16-byte row pitch, when the bias rows themselves are not
+  w.has_bias_pad = w.has_bias_t && s->n % 8 != 0;
+  w.bias_pad_off = off;
+  if (w.has_bias_pad) off = align_up(off + bias_copy, 256);
   w.partial_off = off;
   if (plan.db_row_splits > 1) off = align_up(off + dbb * plan.db_row_splits, 256);
   w.total = off;
@@ -142,10 +174,10 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   if (rc) return rc;
   *p = trifast_plan{};
   const bool half = s->dtype != TRIFAST_F32;
-  // tcgen05 path: 16-bit inputs, d in {32, 64}; the bias tile comes through TMA,
-  // whose row pitch must be a multiple of 16 bytes (n % 8 == 0), and problems
-  // smaller than one 128-wide tile gain nothing from it.
-  const bool tc_ok = half && (s->d == 32 || s->d == 64) && (s->n % 8 == 0) && s->n >= 128;
+  // tcgen05 path: 16-bit inputs, d in {32, 64}; problems smaller than one 128-wide
+  // tile gain nothing from it.  (n % 8 != 0 runs on it through a padded bias copy in
+  // the workspace: TMA needs a 16-byte row pitch.)
+  const bool tc_ok = half && (s->d == 32 || s->d == 64) && s->n >= 128;
   int kernel = s->kernel;
   if (kernel == TRIFAST_KERNEL_AUTO) kernel = tc_ok ? TRIFAST_KERNEL_TCGEN05 : TRIFAST_KERNEL_SIMT;
   if (kernel == TRIFAST_KERNEL_TCGEN05 && !tc_ok) return TRIFAST_ERR_KERNEL_CHOICE;
@@ -218,8 +250,10 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->delta = (float*)(base + w.delta_off);
   a->neg_lse2 = (float*)(base + w.nlse_off);
   a->bias_t = w.has_bias_t ? (void*)(base + w.bias_t_off) : nullptr;
+  a->bias_pad = w.has_bias_pad ? (void*)(base + w.bias_pad_off) : nullptr;
   a->rowfull = (uint8_t*)(base + w.rowfull_off);
   a->maskbits = (uint32_t*)(base + w.maskbits_off);
+  a->maskbits_lin = a->maskbits + (size_t)shape->batch * shape->n_rows * w.mask_words;
   a->mask_words = w.mask_words;
   a->db_f32 = (float*)(base + w.db_off);
   a->db_partials = (float*)(base + w.partial_off);
@@ -271,9 +305,16 @@ size_t trifast_backward_workspace_bytes(const trifast_shape* shape) {
   return carve(shape, plan).total;
 }
 
+size_t trifast_forward_workspace_bytes(const trifast_shape* shape) {
+  trifast_plan plan;
+  if (pick_plan(shape, &plan)) return 0;
+  return carve_fwd(shape, plan).total;
+}
+
 int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifast_t5* k,
                     const trifast_t5* v, const trifast_t4* bias, const trifast_mask* mask,
-                    const trifast_t5* o, float* lse, void* stream) {
+                    const trifast_t5* o, float* lse, void* workspace, size_t workspace_bytes,
+                    void* stream) {
   int rc = check_shape(shape);
   if (rc) return rc;
   if ((rc = check_t5(q, shape)) || (rc = check_t5(k, shape)) || (rc = check_t5(v, shape)) ||
@@ -282,6 +323,9 @@ int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifa
   if (!lse) return TRIFAST_ERR_NULL;
   Common c;
   if ((rc = common_setup(shape, &c))) return rc;
+  const FwdWorkspace w = carve_fwd(shape, c.plan);
+  if (w.total && (!workspace || workspace_bytes < w.total)) return TRIFAST_ERR_WORKSPACE;
+  if (w.total && (((uintptr_t)workspace) & 255)) return TRIFAST_ERR_ALIGN;
   FwdArgs a{};
   a.q = make_view(q);
   a.k = make_view(k);
@@ -293,12 +337,20 @@ int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifa
   a.dm = c.dm;
   a.dtype = shape->dtype;
   a.status = c.status;
+  a.mask_words = w.mask_words;
+  if (w.total) {
+    char* base = (char*)workspace;
+    a.rowfull = (uint8_t*)(base + w.rowfull_off);
+    a.maskbits = (uint32_t*)(base + w.maskbits_off);
+    a.bias_pad = (void*)(base + w.bias_pad_off);
+  }
   cudaStream_t s = (cudaStream_t)stream;
   if (c.plan.kernel == TRIFAST_KERNEL_TCGEN05) {
     if (!tc_forward_supported(c.dm, shape->dtype, &a)) {
       if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
       return cuda_rc(simt_forward(a, s));
     }
+    if (w.total && (rc = cuda_rc(fwd_prepare(a, s)))) return rc;
     return cuda_rc(tc_forward(a, c.plan, s));
   }
   return cuda_rc(simt_forward(a, s));

@@ -28,6 +28,7 @@ struct MaskView {
 
 struct Dims {
   int batch, heads, n, n_rows, d;
+  int n_pad;       // n rounded up to 8: row pitch (elements) of workspace vectors and bias copies
   float scale;     // d^-0.5
   float sentinel;  // finfo(dtype).min as float: stored as lse of fully masked rows
 };

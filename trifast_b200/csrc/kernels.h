@@ -10,6 +10,11 @@ struct FwdArgs {
   View4 bias;
   MaskView mask;
   float* lse;
+  // forward workspace (tensor-core path with n % 8 != 0 only; null otherwise)
+  void* bias_pad;        // (b, h, j, n_pad) copy of the bias with a 16-byte row pitch
+  uint8_t* rowfull;      // (b, n_rows)
+  uint32_t* maskbits;    // (b, n_rows, mask_words)
+  int mask_words;
   Dims dm;
   int dtype;
   unsigned int* status;  // device status word
@@ -20,11 +25,16 @@ struct BwdArgs {
   View4 bias;
   MaskView mask;
   const float* lse;
-  float* delta;          // (b, h, n_rows, n) fp32, in the workspace
-  float* neg_lse2;       // (b, h, n_rows, n) fp32: -lse * log2(e), in the workspace
-  void* bias_t;          // (b, h, k, j) transposed bias copy in the input dtype, or null
+  float* delta;          // (b, h, n_rows, n_pad) fp32, in the workspace
+  float* neg_lse2;       // (b, h, n_rows, n_pad) fp32: -lse * log2(e), in the workspace
+  void* bias_t;          // (b, h, k, n_pad) transposed bias copy in the input dtype, or null
+  void* bias_pad;        // (b, h, j, n_pad) bias copy with a 16-byte row pitch (n % 8 != 0), or null
   uint8_t* rowfull;      // (b, n_rows): 1 = every key of the row is masked
-  uint32_t* maskbits;    // (b, n_rows, mask_words): bit set = key dropped or beyond n
+  // (b, n_rows, mask_words): bit set = key dropped or beyond n.  Per 128-key chunk c
+  // four words: word c*4 + jb holds, at bit l, key c*128 + 4*l + jb.
+  uint32_t* maskbits;
+  // same bits in key order: word w holds, at bit l, key 32 * w + l
+  uint32_t* maskbits_lin;
   int mask_words;        // 4 * ceil(n / 128)
   float* db_f32;         // (b, h, n, n) fp32 result of the row reduction
   float* db_partials;    // (splits, b, h, n, n) fp32, used when splits > 1
@@ -36,7 +46,8 @@ struct BwdArgs {
 
 // CUDA-core kernels (simt_kernels.cu): any dtype, any n, d in {16, 32, 64, 128}.
 cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s);
-cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s);   // delta + rowfull (all paths)
+cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s);   // delta, row flags, masks, bias copies
+cudaError_t fwd_prepare(const FwdArgs& a, cudaStream_t s);   // row flags, masks, padded bias
 cudaError_t simt_bwd_db(const BwdArgs& a, cudaStream_t s);
 cudaError_t simt_bwd_dq(const BwdArgs& a, cudaStream_t s);
 cudaError_t simt_bwd_dkv(const BwdArgs& a, cudaStream_t s);

@@ -81,7 +81,7 @@ __device__ __forceinline__ void axpy_smem(float a, const float* sm, float* reg) 
 // rowfull[b, i] = 1 when every key of pair row i is masked.
 // ---------------------------------------------------------------------------
 __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowfull,
-                               uint32_t* maskbits, int mask_words) {
+                               uint32_t* maskbits, uint32_t* maskbits_lin, int mask_words) {
   const int bi = blockIdx.x;
   const int b = bi / n_rows, i = bi % n_rows;
   const uint8_t* row = mask.p + b * mask.sb + (int64_t)i * mask.si;
@@ -89,14 +89,40 @@ __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowful
   for (int k = threadIdx.x; k < n; k += blockDim.x) open |= (row[k] == 0);
   open = __syncthreads_or(open);
   if (threadIdx.x == 0) rowfull[bi] = open ? 0 : 1;
-  // Packed key mask (bit set = key dropped or beyond n).  A fully masked row
-  // keeps all n keys with uniform weight, so only the keys beyond n stay set.
-  for (int k0 = 0; k0 < mask_words * 32; k0 += blockDim.x) {
-    const int k = k0 + threadIdx.x;
-    const int dropped = (k < n) ? (open ? (row[k] != 0) : 0) : 1;
-    const unsigned bits = __ballot_sync(0xffffffffu, dropped);
-    if ((threadIdx.x & 31) == 0) maskbits[(int64_t)bi * mask_words + (k >> 5)] = bits;
+  // Packed key mask (bit set = key dropped or beyond n).  A fully masked row keeps
+  // all n keys with uniform weight, so only the keys beyond n stay set.  Layout per
+  // 128-key chunk c: word c*4 + jb holds, at bit l, key c*128 + 4*l + jb (the order
+  // in which a warp reading four mask bytes per lane produces the words).
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = warp; c < mask_words / 4; c += blockDim.x >> 5) {
+#pragma unroll
+    for (int jb = 0; jb < 4; ++jb) {
+      const int k = c * 128 + 4 * lane + jb;
+      const int dropped = (k < n) ? (open ? (row[k] != 0) : 0) : 1;
+      const unsigned bits = __ballot_sync(0xffffffffu, dropped);
+      if (lane == 0) maskbits[(int64_t)bi * mask_words + c * 4 + jb] = bits;
+    }
   }
+  // The same bits in key order (word w, bit l: key 32 * w + l), when asked for.
+  if (maskbits_lin) {
+    for (int w = warp; w < mask_words; w += blockDim.x >> 5) {
+      const int k = w * 32 + lane;
+      const int dropped = (k < n) ? (open ? (row[k] != 0) : 0) : 1;
+      const unsigned bits = __ballot_sync(0xffffffffu, dropped);
+      if (lane == 0) maskbits_lin[(int64_t)bi * mask_words + w] = bits;
+    }
+  }
+}
+
+// bias_pad[b, h, j, 0..n_pad) = bias[b, h, j, 0..n) (pad = 0): a copy whose row pitch
+// is a multiple of 16 bytes, as TMA needs, for n % 8 != 0.
+__global__ void bias_pad_kernel(View4 bias, uint16_t* out, int heads, int n, int n_pad) {
+  const int bh = blockIdx.z, b = bh / heads, h = bh % heads;
+  const int j = blockIdx.y;
+  const uint16_t* src = (const uint16_t*)bias.p + b * bias.sb + h * bias.sh + (int64_t)j * bias.sj;
+  uint16_t* dst = out + ((int64_t)bh * n + j) * n_pad;
+  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < n_pad; k += gridDim.x * blockDim.x)
+    dst[k] = (k < n) ? src[k] : (uint16_t)0;
 }
 
 // ---------------------------------------------------------------------------
@@ -138,18 +164,19 @@ __global__ void delta_kernel(View5 o, View5 d_o, const float* lse, float* delta,
 #pragma unroll
   for (int m = G / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
   if (valid && part == 0) {
-    delta[idx] = acc;
-    neg_lse2[idx] = -lse[idx] * 1.4426950408889634f;
+    const int64_t out = (idx / dm.n) * dm.n_pad + idx % dm.n;  // row pitch n_pad
+    delta[out] = acc;
+    neg_lse2[out] = -lse[idx] * 1.4426950408889634f;
   }
 }
 
-// bias_t[b, h, k, j] = bias[b, h, j, k] for 2-byte elements (the dk/dv kernel reads
+// bias_t[b, h, k, j] = bias[b, h, j, k] (row pitch n_pad) for 2-byte elements (the dk/dv kernel reads
 // the bias with keys on the rows).
-__global__ void bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int n) {
+__global__ void bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int n, int n_pad) {
   __shared__ uint16_t tile[32][33];
   const int bh = blockIdx.z, b = bh / heads, h = bh % heads;
   const uint16_t* src = (const uint16_t*)bias.p + b * bias.sb + h * bias.sh;
-  uint16_t* dst = out + (int64_t)bh * n * n;
+  uint16_t* dst = out + (int64_t)bh * n * n_pad;
   const int j0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
   for (int r = threadIdx.y; r < 32; r += 8) {
     const int j = j0 + r, k = k0 + threadIdx.x;
@@ -158,7 +185,7 @@ __global__ void bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int 
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += 8) {
     const int k = k0 + r, j = j0 + threadIdx.x;
-    if (j < n && k < n) dst[(int64_t)k * n + j] = tile[threadIdx.x][r];
+    if (j < n && k < n) dst[(int64_t)k * n_pad + j] = tile[threadIdx.x][r];
   }
 }
 
@@ -270,7 +297,9 @@ __global__ void __launch_bounds__(BJ) simt_dq_kernel(View5 q, View5 k, View5 v, 
     }
   }
   const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + (jvalid ? j : 0);
-  const float my_lse = lse[stat], my_delta = delta[stat];
+  const float my_lse = lse[stat];
+  const float my_delta =
+      delta[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * dm.n_pad + (jvalid ? j : 0)];
   const T* brow = row4<T>(bias, b, h, jvalid ? j : 0);
 
   for (int k0 = 0; k0 < n; k0 += BK) {
@@ -348,7 +377,7 @@ __global__ void __launch_bounds__(BKT) simt_dkv_kernel(View5 q, View5 k, View5 v
     stage_tile<T, D, BJT, BKT>(Gs, valid, [&](int r) { return row5<T>(d_o, b, h, i, j0 + r); });
     for (int t = tid; t < BJT; t += BKT) {
       Ls[t] = (t < valid) ? lse[stat0 + j0 + t] : 0.f;
-      Ds[t] = (t < valid) ? delta[stat0 + j0 + t] : 0.f;
+      Ds[t] = (t < valid) ? delta[stat0 / n * dm.n_pad + j0 + t] : 0.f;
     }
     __syncthreads();
     if (masked) continue;  // exactly zero weight: no contribution to dk, dv
@@ -438,7 +467,7 @@ __global__ void __launch_bounds__(256) simt_db_kernel(View5 q, View5 k, View5 v,
       if (c0 == 0) {
         if (tid < TJ) {
           Ls[tid] = (tid < vj) ? lse[stat0 + j0 + tid] : 0.f;
-          Ds[tid] = (tid < vj) ? delta[stat0 + j0 + tid] : 0.f;
+          Ds[tid] = (tid < vj) ? delta[stat0 / n * dm.n_pad + j0 + tid] : 0.f;
         } else if (tid < TJ + TK) {
           const int t = tid - TJ;
           Ms[t] = (t < vk) ? (row_full ? 0 : mask.p[b * mask.sb + (int64_t)i * mask.si + k0 + t]) : 1;
@@ -545,10 +574,15 @@ cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s) {
 cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
   rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
-                                                      a.mask_words);
+                                                      a.maskbits_lin, a.mask_words);
   if (a.bias_t) {
     dim3 grid((dm.n + 31) / 32, (dm.n + 31) / 32, dm.batch * dm.heads);
-    bias_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n);
+    bias_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n,
+                                                       dm.n_pad);
+  }
+  if (a.bias_pad) {
+    dim3 grid(1, dm.n, dm.batch * dm.heads);
+    bias_pad_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_pad, dm.heads, dm.n, dm.n_pad);
   }
   return dispatch(a.dtype, dm.d, [&](auto* tp, auto dc) {
     using T = std::remove_pointer_t<decltype(tp)>;
@@ -559,6 +593,15 @@ cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
     delta_kernel<T, D><<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a.o, a.d_o, a.lse, a.delta,
                                                                        a.neg_lse2, dm);
   });
+}
+
+cudaError_t fwd_prepare(const FwdArgs& a, cudaStream_t s) {
+  const Dims& dm = a.dm;
+  rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
+                                                      nullptr, a.mask_words);
+  dim3 grid(1, dm.n, dm.batch * dm.heads);
+  bias_pad_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_pad, dm.heads, dm.n, dm.n_pad);
+  return cudaGetLastError();
 }
 
 cudaError_t simt_bwd_db(const BwdArgs& a, cudaStream_t s) {

@@ -246,7 +246,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     }
     if (ok && j < n) {
       float* dst = out + (((int64_t)split * dm.batch * dm.heads + bh) * n + j) * n + key0;
-      if (key0 + 32 <= n) {
+      if (key0 + 32 <= n && (n & 3) == 0) {
 #pragma unroll
         for (int c = 0; c < 32; c += 4)
           *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
@@ -293,9 +293,9 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
   if (!map5(&mq, a.q) || !map5(&mdo, a.d_o) || !map5(&mk, a.k) || !map5(&mv, a.v))
     return cudaErrorInvalidValue;
   {
-    const uint64_t n = dm.n, rows = dm.n_rows;
+    const uint64_t n = dm.n, np = dm.n_pad, rows = dm.n_rows;
     const uint64_t dims4[4] = {n, rows, (uint64_t)dm.heads, (uint64_t)dm.batch};
-    const uint64_t st[3] = {n * 4, n * rows * 4, n * rows * dm.heads * 4};
+    const uint64_t st[3] = {np * 4, np * rows * 4, np * rows * dm.heads * 4};
     const uint32_t box4[4] = {128, 1, 1, 1};
     if (!make_tensor_map_f32(&mnl, 4, a.neg_lse2, dims4, st, box4) ||
         !make_tensor_map_f32(&mdl, 4, a.delta, dims4, st, box4))
@@ -309,7 +309,7 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
   dim3 grid(t * t, a.splits, dm.batch * dm.heads);
   float* out = a.splits > 1 ? a.db_partials : a.db_f32;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mnl, mdl, a.bias, a.rowfull,
-                                              a.maskbits, a.mask_words, out, a.splits, dm, a.status);
+                                              a.maskbits_lin, a.mask_words, out, a.splits, dm, a.status);
   return cudaGetLastError();
 }
 
@@ -317,7 +317,7 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
 
 cudaError_t tc_bwd_db(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
-  if (!a.neg_lse2 || !a.maskbits) return cudaErrorInvalidValue;
+  if (!a.neg_lse2 || !a.maskbits_lin) return cudaErrorInvalidValue;
   if (a.dm.d == 32)
     return bf16 ? launch_db<__nv_bfloat16, 32, 4>(a, s) : launch_db<__half, 32, 4>(a, s);
   return bf16 ? launch_db<__nv_bfloat16, 64, 3>(a, s) : launch_db<__half, 64, 3>(a, s);

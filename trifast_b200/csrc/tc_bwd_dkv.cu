@@ -460,18 +460,18 @@ cudaError_t launch_dkv(const BwdArgs& a, cudaStream_t stream) {
   if (!map5(&mk, a.k, box_kv) || !map5(&mv, a.v, box_kv) || !map5(&mq, a.q, box_q) ||
       !map5(&mdo, a.d_o, box_q))
     return cudaErrorInvalidValue;
-  {  // transposed bias copy: (b, h, k, j) contiguous
-    const uint64_t n = dm.n;
+  {  // transposed bias copy: (b, h, k, j) with row pitch n_pad
+    const uint64_t n = dm.n, np = dm.n_pad;
     const uint64_t dims4[4] = {n, n, (uint64_t)dm.heads, (uint64_t)dm.batch};
-    const uint64_t st[3] = {n * eb, n * n * eb, n * n * dm.heads * eb};
+    const uint64_t st[3] = {np * eb, n * np * eb, n * np * dm.heads * eb};
     const uint32_t box4[4] = {(uint32_t)kBJ, 128, 1, 1};
     if (!make_tensor_map(&mbt, bf16, 4, a.bias_t, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
       return cudaErrorInvalidValue;
   }
-  {  // -lse * log2(e) and delta: (b, h, rows, n) fp32 contiguous, made by the prepare step
-    const uint64_t n = dm.n, rows = dm.n_rows;
+  {  // -lse * log2(e) and delta: (b, h, rows, n_pad) fp32, made by the prepare step
+    const uint64_t n = dm.n, np = dm.n_pad, rows = dm.n_rows;
     const uint64_t dims4[4] = {n, rows, (uint64_t)dm.heads, (uint64_t)dm.batch};
-    const uint64_t st[3] = {n * 4, n * rows * 4, n * rows * dm.heads * 4};
+    const uint64_t st[3] = {np * 4, np * rows * 4, np * rows * dm.heads * 4};
     const uint32_t box4[4] = {(uint32_t)kBJ, 1, 1, 1};
     if (!make_tensor_map_f32(&mlse, 4, a.neg_lse2, dims4, st, box4) ||
         !make_tensor_map_f32(&mdelta, 4, a.delta, dims4, st, box4))

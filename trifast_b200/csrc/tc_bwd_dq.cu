@@ -59,8 +59,8 @@ struct DqCfg {
   static constexpr int kSbo = 8 * kRowBytes;
   static int mask_words(int n) { return ((n + 127) / 128) * 4; }
   static int smem_bytes(int n) {
-    const int head = (kHeaderBytes + 4 * R * mask_words(n) * 4 + 1023) / 1024 * 1024;
-    return 1024 + head + kTilesBytes;
+    (void)n;
+    return 1024 + 1024 + kTilesBytes;
   }
 };
 
@@ -73,8 +73,9 @@ __global__ void __launch_bounds__(384, 1)
 tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_b, View5 dq, const float* __restrict__ lse,
-             const float* __restrict__ delta, const uint8_t* __restrict__ rowfull, MaskView mask,
-             Dims dm, ItemGrid items, unsigned int* status) {
+             const float* __restrict__ delta, const uint8_t* __restrict__ rowfull,
+             const uint32_t* __restrict__ maskbits, int mask_words, Dims dm, ItemGrid items,
+             unsigned int* status) {
   using Cfg = DqCfg<D, NS>;
   constexpr int R = Cfg::R;
   constexpr int IN_FULL = 0, IN_EMPTY = 1, FULL = 2, EMPTY = FULL + NS, S_FULL = EMPTY + NS,
@@ -88,12 +89,10 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
   uint8_t* gbase = smem_raw + (base - raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
-  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][mask_words]
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
-  const int mwords = ((n + 127) / 128) * 4;
-  const uint32_t tiles_off = (kHeaderBytes + 4 * R * mwords * 4 + 1023u) & ~1023u;
+  constexpr uint32_t tiles_off = 1024;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kQBytes; };
@@ -259,7 +258,6 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
       const uint32_t tS = tmem_base + lane_base + r * 256;
       const uint32_t tDP = tS + 64, tDS = tS + 128, tDQ = tS + 160;
-      uint32_t* mb = maskbits + warp * mwords;  // this warp's own copy: no cross-warp sync
       const float c1 = dm.scale * kLog2e;
       const float uniform = 1.f / (float)n;
 
@@ -273,32 +271,27 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         const int j = im.jt * kBJ + t;
         const bool row_full = rowfull[b * dm.n_rows + i] != 0;
 
-        // Key mask of row i as bit words (bit set = key dropped or beyond n; none
-        // dropped inside n on a fully masked row).  Lane l reads keys 4l .. 4l+3 of a
-        // 128-key chunk as one word; word jb of the chunk holds, at bit l, key 4l + jb.
-        {
-          const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
-          for (int c = 0; c < mwords / 4; ++c) {
-            const int key4 = c * 128 + 4 * lane;
-            uint32_t u = 0x01010101u;
-            if (key4 < n) u = row_full ? 0u : __ldg(reinterpret_cast<const uint32_t*>(mrow + key4));
-#pragma unroll
-            for (int jb = 0; jb < 4; ++jb) {
-              const uint32_t bits = __ballot_sync(0xffffffffu, ((u >> (8 * jb)) & 0xffu) != 0u);
-              if (lane == 0) mb[c * 4 + jb] = bits;
-            }
-          }
-          __syncwarp();
-        }
+        // Key mask of row i as packed words made by the prepare step (bit set = key
+        // dropped or beyond n; none dropped inside n on a fully masked row).  Per 128-key
+        // chunk c: word c*4 + jb holds, at bit l, key c*128 + 4*l + jb.
+        const uint32_t* mb = maskbits + ((int64_t)b * dm.n_rows + i) * mask_words;
         const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + min(j, n - 1);
         const float neg_lse2 = -lse[stat] * kLog2e;
-        const float my_delta = delta[stat];
+        const float my_delta =
+            delta[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * dm.n_pad + min(j, n - 1)];
 
         auto key_loop = [&](auto row_full_tag) {
           constexpr bool kRowFull = decltype(row_full_tag)::value;
           for (int kt = 0; kt < nkt; ++kt, ++g) {
             const int s = g % NS;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
+            // S/dP of this tile and its bias stage: S_FULL implies FULL (the MMA that made
+            // S read K from the same stage), so both tests succeed together and their
+            // latencies overlap instead of adding up.
+            {
+              const bool a = mbar_wait(bar(S_FULL + r), g & 1, abort_flag);
+              const bool c = mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag);
+              ok = __all_sync(0xffffffffu, a && c);
+            }
             if (!ok) break;
             tc_fence_after();
             float x[64], gd[64];
@@ -309,28 +302,24 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
               tmem_ld32(tS + 32, xr + 32);
               tmem_ld32(tDP + 0, gr + 0);
               tmem_ld32(tDP + 32, gr + 32);
-              tmem_wait_ld();
             }
+            // while the TMEM loads are in flight: mask words of this 64-key tile (the
+            // tile is half (kt & 1) of chunk kt >> 1; column c is position
+            // pos = (kt & 1) * 64 + c: bit (pos >> 2) of word (pos & 3)) and the test that
+            // the dQ MMA of the previous key tile no longer reads the dS columns
+            uint32_t mw[4];
+#pragma unroll
+            for (int jb = 0; jb < 4; ++jb)
+              mw[jb] = (__ldg(mb + (kt >> 1) * 4 + jb) >> ((kt & 1) * 16)) & 0xffffu;
+            const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
+            // (a non-blocking look now; if it is not done yet the wait happens after the pass)
+            const bool dq_done =
+                __all_sync(0xffffffffu, (kt == 0) || mbar_test_wait(bar(DQ_DONE + r), (g - 1) & 1));
+            tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(S_FREE + r));
 
-            // mask words of this 64-key tile: the tile is half (kt & 1) of chunk kt >> 1;
-            // column c is position pos = (kt & 1) * 64 + c: bit (pos >> 2) of word (pos & 3)
-            uint32_t mw[4];
-#pragma unroll
-            for (int jb = 0; jb < 4; ++jb) mw[jb] = (mb[(kt >> 1) * 4 + jb] >> ((kt & 1) * 16)) & 0xffffu;
-            const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
-
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
-            if (!ok) break;
-            // The two slots take turns in the pass below (it is MUFU-bound), so that one
-            // slot's waits, TMEM loads and stores overlap the other's exponentials.
-            if (kSlotToken) {
-              ok = __all_sync(0xffffffffu,
-                              mbar_wait(bar(TOKEN + r), (r == 0) ? ((g & 1) ^ 1) : (g & 1), abort_flag));
-              if (!ok) break;
-            }
             // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
             // exponential (MUFU), dS and the 16-bit pack.
             uint32_t pk[32];
@@ -370,7 +359,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
               if (kSlotToken) mbar_arrive(bar(TOKEN + (r ^ 1)));
             }
 
-            if (kt > 0) {  // the dQ MMA of the previous key tile still reads the dS columns
+            if (!dq_done) {
               ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));
               if (!ok) break;
             }
@@ -455,10 +444,14 @@ cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
       !map5(&mv, a.v, box_k))
     return cudaErrorInvalidValue;
   {
-    const uint64_t dims4[4] = {(uint64_t)dm.n, (uint64_t)dm.n, (uint64_t)dm.heads, (uint64_t)dm.batch};
-    const uint64_t st[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    // the bias itself when its rows are 16-byte pitched, else the padded copy
+    const uint64_t n = dm.n, np = dm.n_pad;
+    const uint64_t dims4[4] = {n, n, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st_user[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    const uint64_t st_pad[3] = {np * eb, n * np * eb, n * np * dm.heads * eb};
     const uint32_t box4[4] = {(uint32_t)kBK, 128, 1, 1};
-    if (!make_tensor_map(&mbias, bf16, 4, a.bias.p, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (!make_tensor_map(&mbias, bf16, 4, a.bias_pad ? a.bias_pad : (void*)a.bias.p, dims4,
+                         a.bias_pad ? st_pad : st_user, box4, CU_TENSOR_MAP_SWIZZLE_128B))
       return cudaErrorInvalidValue;
   }
   const int smem = Cfg::smem_bytes(dm.n);
@@ -472,7 +465,7 @@ cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
   const int sms = sm_count_dq();
   const int grid = items.total < sms ? items.total : sms;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mbias, a.dq, a.lse, a.delta,
-                                              a.rowfull, a.mask, dm, items, a.status);
+                                              a.rowfull, a.maskbits, a.mask_words, dm, items, a.status);
   return cudaGetLastError();
 }
 
@@ -482,13 +475,12 @@ bool tc_backward_supported(const BwdArgs& a) {
   const Dims& dm = a.dm;
   if (a.dtype != TRIFAST_BF16 && a.dtype != TRIFAST_F16) return false;
   if (dm.d != 32 && dm.d != 64) return false;
-  if (dm.n % 8 != 0 || dm.n < 128) return false;
-  const int smem = (dm.d == 32) ? DqCfg<32, 4>::smem_bytes(dm.n) : DqCfg<64, 3>::smem_bytes(dm.n);
-  if (smem > kSmemLimit) return false;
-  if ((a.bias.sj * 2) % 16 || (a.bias.sh * 2) % 16 || (a.bias.sb * 2) % 16) return false;
-  if (((uintptr_t)a.bias.p) & 15) return false;
-  // the key mask is read four bytes at a time
-  if (((uintptr_t)a.mask.p) & 3 || a.mask.sb % 4 || a.mask.si % 4) return false;
+  if (dm.n < 128) return false;
+  if (!a.maskbits || !a.rowfull || !a.delta || !a.neg_lse2) return false;
+  // the bias goes through TMA: 16-byte row pitch, or the padded copy from the workspace
+  const bool bias_tma_ok = !(((uintptr_t)a.bias.p) & 15) && (a.bias.sj * 2) % 16 == 0 &&
+                           (a.bias.sh * 2) % 16 == 0 && (a.bias.sb * 2) % 16 == 0;
+  if (!bias_tma_ok && !a.bias_pad) return false;
   return tc::get_encode_tiled() != nullptr;
 }
 

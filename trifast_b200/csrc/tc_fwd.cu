@@ -94,7 +94,8 @@ template <typename T, int D, int R, int NS>
 __global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
-              View5 o, float* __restrict__ lse, MaskView mask, Dims dm, ItemGrid items,
+              View5 o, float* __restrict__ lse, MaskView mask, const uint8_t* __restrict__ ws_rowfull,
+              const uint32_t* __restrict__ ws_maskbits, int ws_mask_words, Dims dm, ItemGrid items,
               unsigned int* status) {
   using Cfg = FwdCfg<D, R, NS>;
   static_assert(R == 2, "two slots: the exp phases alternate between them");
@@ -291,7 +292,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       // reads keys 4l .. 4l+3 of a 128-key chunk as one word; word j of the chunk
       // then holds, at bit l, key 4l + j.
       bool row_full;
-      {
+      const uint32_t* mbr = mb;  // where this row's mask words are read from
+      if (ws_maskbits != nullptr) {
+        // made by the prepare step (n % 8 != 0: the mask rows are not word-aligned)
+        mbr = ws_maskbits + ((int64_t)b * dm.n_rows + i) * ws_mask_words;
+        row_full = ws_rowfull[b * dm.n_rows + i] != 0;
+      } else {
         const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
         uint32_t open = 0;
         for (int c = 0; c < nkt; ++c) {
@@ -339,11 +345,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         uint32_t mw[4];
 #pragma unroll
         for (int jb = 0; jb < 4; ++jb) {
-          if (kRowFull) {  // only keys beyond n stay dropped
-            const int groups = (n - kt * kBK) / 4;
-            mw[jb] = groups >= 32 ? 0u : (groups <= 0 ? 0xffffffffu : ~((1u << groups) - 1u));
+          if (kRowFull) {  // only keys beyond n stay dropped: key 4l + jb of the chunk
+            const int rem = n - kt * kBK - jb;             // keys 4l + jb < n  <=>  l < ceil(rem / 4)
+            const int groups = rem <= 0 ? 0 : (rem + 3) / 4;
+            mw[jb] = groups >= 32 ? 0u : ~((1u << groups) - 1u);
           } else {
-            mw[jb] = mb[kt * 4 + jb];
+            mw[jb] = mbr[kt * 4 + jb];
           }
         }
         const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
@@ -533,10 +540,14 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
   };
   if (!map5(&mq, a.q) || !map5(&mk, a.k) || !map5(&mv, a.v)) return cudaErrorInvalidValue;
   {
-    const uint64_t dims4[4] = {(uint64_t)dm.n, (uint64_t)dm.n, (uint64_t)dm.heads, (uint64_t)dm.batch};
-    const uint64_t st[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    // the bias itself when its rows are 16-byte pitched, else the padded copy
+    const uint64_t n = dm.n, np = dm.n_pad;
+    const uint64_t dims4[4] = {n, n, (uint64_t)dm.heads, (uint64_t)dm.batch};
+    const uint64_t st_user[3] = {(uint64_t)a.bias.sj * eb, (uint64_t)a.bias.sh * eb, (uint64_t)a.bias.sb * eb};
+    const uint64_t st_pad[3] = {np * eb, n * np * eb, n * np * dm.heads * eb};
     const uint32_t box4[4] = {64, 128, 1, 1};
-    if (!make_tensor_map(&mbias, bf16, 4, a.bias.p, dims4, st, box4, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (!make_tensor_map(&mbias, bf16, 4, a.bias_pad ? a.bias_pad : (void*)a.bias.p, dims4,
+                         a.bias_pad ? st_pad : st_user, box4, CU_TENSOR_MAP_SWIZZLE_128B))
       return cudaErrorInvalidValue;
   }
   const int smem = Cfg::smem_bytes(dm.n);
@@ -548,8 +559,8 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
   items.nrp = (dm.n_rows + R - 1) / R;
   items.total = items.njt * items.nrp * dm.batch * dm.heads;
   const int grid = items.total < sm_count() ? items.total : sm_count();
-  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, dm, items,
-                                              a.status);
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, a.rowfull,
+                                              a.maskbits, a.mask_words, dm, items, a.status);
   return cudaGetLastError();
 }
 
@@ -612,15 +623,20 @@ bool make_tensor_map_f32(CUtensorMap* map, int rank, void* base, const uint64_t*
 bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
   if (dtype != TRIFAST_BF16 && dtype != TRIFAST_F16) return false;
   if (dm.d != 32 && dm.d != 64) return false;
-  if (dm.n % 8 != 0 || dm.n < 128) return false;
+  if (dm.n < 128) return false;
   const int smem = (dm.d == 32) ? FwdCfg<32, 2, 3>::smem_bytes(dm.n) : FwdCfg<64, 2, 2>::smem_bytes(dm.n);
   if (smem > kSmemLimit) return false;
   if (a) {
-    if ((a->bias.sj * 2) % 16 || (a->bias.sh * 2) % 16 || (a->bias.sb * 2) % 16) return false;
-    if (((uintptr_t)a->bias.p) & 15) return false;
     if (((uintptr_t)a->o.p) & 15 || (a->o.sj * 2) % 16) return false;
-    // the key mask is read four bytes at a time
-    if (((uintptr_t)a->mask.p) & 3 || a->mask.sb % 4 || a->mask.si % 4) return false;
+    const bool have_ws = a->bias_pad && a->maskbits && a->rowfull;
+    if (!have_ws) {
+      // without the prepared copies the bias goes through TMA as it is (16-byte row
+      // pitch) and the key mask is read four bytes at a time
+      if (dm.n % 8 != 0) return false;
+      if ((a->bias.sj * 2) % 16 || (a->bias.sh * 2) % 16 || (a->bias.sb * 2) % 16) return false;
+      if (((uintptr_t)a->bias.p) & 15) return false;
+      if (((uintptr_t)a->mask.p) & 3 || a->mask.sb % 4 || a->mask.si % 4) return false;
+    }
   }
   return tc::get_encode_tiled() != nullptr;
 }
