@@ -10,7 +10,7 @@ includes the NCCL all-reduce of the bias gradient.  Rank 0 prints ONE JSON line.
 
 Keys beyond the usual ones:
   value / ms_per_step : kernels only, inputs resident in HBM, CUDA events, max over ranks
-  e2e                 : the same step through the public autograd API with pinned-host
+  e2e                 : the same step through the package's host-resident API with pinned-host
                         inputs copied in and o, dq, dk, dv, db copied out every step
   roofline            : the dominant kernel phase against the measured bf16 tensor peak
   phases_ms           : forward / db / dq+dk+dv phase times (CUDA events, N = 1)
@@ -310,28 +310,23 @@ def run_native(args, w):
     step._lib.check(rc, "device status after the timed region")
 
     # ---- end to end through the public API with host buffers ---------------------------
+    # Pinned host tensors in, pinned host tensors out, through the host-resident entry
+    # point of the package (trifast_b200.host): every step copies this rank's q, k, v,
+    # dO, mask and the bias to the GPU and o, dq, dk, dv, db back, in blocks of rows
+    # that overlap with the kernels.
+    from trifast_b200.host import HostPipeline
     host = [t.cpu().pin_memory() for t in (q, k, v, b, m, do)]
+    bs_, h_, rows_, n_, d_ = q.shape
+    pipe = HostPipeline(bs_, h_, n_, d_, q.dtype, dev, rows=rows_, chunk_rows=args.e2e_chunk_rows,
+                        backward=w.backward)
     outs_host = None
+    group = dist.group.WORLD if world > 1 else None
 
     def e2e_step():
         nonlocal outs_host
-        dq_, dk_, dv_, db_, dm_, ddo_ = (t.to(dev, non_blocking=True) for t in host)
-        for t in (dq_, dk_, dv_, db_):
-            t.requires_grad_(w.backward)
-        if world > 1:
-            o = triangle_attention_row_sharded(dq_, dk_, dv_, db_, dm_)
-        else:
-            from trifast_b200 import triangle_attention
-            o = triangle_attention(dq_, dk_, dv_, db_, dm_)
-        res = [o]
-        if w.backward:
-            o.backward(ddo_)
-            res += [dq_.grad, dk_.grad, dv_.grad, db_.grad]
-        if outs_host is None:
-            outs_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in res]
-        for dst, src in zip(outs_host, res):
-            dst.copy_(src.detach(), non_blocking=True)
-        return res
+        hq, hk, hv, hb, hm, hdo = host
+        outs_host = pipe.run(hq, hk, hv, hb, hm, do=hdo if w.backward else None, out=outs_host,
+                             group=group)
 
     e2e_iters = max(2, min(args.steps, 5))
     e2e_step()
@@ -344,8 +339,8 @@ def run_native(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t)
     h2d = sum(t.numel() * t.element_size() for t in host)
-    d2h = sum(t.numel() * t.element_size() for t in outs_host)
-    del host, outs_host
+    d2h = sum(t.numel() * t.element_size() for t in outs_host.values())
+    del host, outs_host, pipe
     total_flops = flops_step(w)
 
     # ---- per-phase timing, roofline and the CPU baseline (single GPU only) ------------
@@ -423,6 +418,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="metric_n1024", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunk-rows", type=int, default=64,
+                    help="pair rows per block of the host-resident pipeline (e2e figure)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -1,0 +1,238 @@
+"""Forward + backward for pair tensors that live in pinned host memory.
+
+Pair rows are independent in o, dq, dk and dv, and db is a sum over rows, so a
+step over host-resident q, k, v, dO can run as a pipeline over blocks of rows:
+block c + 1 is copied to the GPU and block c - 1 is copied back while block c
+is computed.  Host-to-device copies, kernels and device-to-host copies run on
+three streams; PCIe carries both directions at once, so a step takes about as
+long as the larger of the two transfers instead of their sum plus the compute.
+The device holds ``slots`` blocks at a time, so n is not limited by HBM either.
+
+The reference (latkins/trifast, src/trifast/torch.py:220-228) takes device
+tensors only; this layer has no counterpart there.  All compute goes through
+the same C-ABI entry points as ``trifast_b200.triangle_attention``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+_NAMES_IN = ("q", "k", "v", "do")
+_NAMES_OUT = ("o", "dq", "dk", "dv")
+
+
+def _check_host5(name, t, shape, dtype):
+    if t.is_cuda or not t.is_pinned():
+        raise ValueError(f"{name} must be a pinned host tensor (torch.Tensor.pin_memory)")
+    if tuple(t.shape) != shape or t.dtype != dtype:
+        raise ValueError(f"{name} must be {shape} {dtype}; got {tuple(t.shape)} {t.dtype}")
+    _, _, rows, n, d = shape
+    if t.stride(4) != 1 or t.stride(3) != d or (rows > 1 and t.stride(2) != n * d):
+        raise ValueError(f"{name}: the (rows, n, d) block of every (batch, head) must be contiguous")
+
+
+class HostPipeline:
+    """Preallocated device buffers and streams for one problem shape.
+
+    ``rows`` is the number of pair rows this process works on (all n of them on
+    one GPU, its shard under ``group``); ``chunk_rows`` of them travel and are
+    computed at a time.
+    """
+
+    def __init__(self, batch: int, heads: int, n: int, d: int, dtype: torch.dtype,
+                 device: torch.device, rows: Optional[int] = None, chunk_rows: int = 64,
+                 slots: int = 3, backward: bool = True):
+        if slots < 2:
+            raise ValueError("at least two slots are needed to overlap copies with compute")
+        self.lib = _lib.load()
+        self.batch, self.heads, self.n, self.d, self.dtype = batch, heads, n, d, dtype
+        self.rows = n if rows is None else rows
+        self.chunk = max(1, min(chunk_rows, self.rows))
+        self.slots, self.backward = slots, backward
+        self.device = torch.device(device)
+        es = torch.empty((), dtype=dtype).element_size()
+        blk = batch * heads * self.chunk * n * d
+        dev = self.device
+        names = _NAMES_IN + _NAMES_OUT if backward else ("q", "k", "v", "o")
+        self._flat = {nm: [torch.empty(blk, dtype=dtype, device=dev) for _ in range(slots)]
+                      for nm in names}
+        self._mask = [torch.empty(batch * self.chunk * n, dtype=torch.uint8, device=dev)
+                      for _ in range(slots)]
+        self._lse = [torch.empty(batch * heads * self.chunk * n, dtype=torch.float32, device=dev)
+                     for _ in range(slots)]
+        self.bias = torch.empty((batch, heads, n, n), dtype=dtype, device=dev)
+        full = _lib.make_shape(batch, heads, n, self.chunk, d, dtype)
+        self._fws_bytes = self.lib.trifast_forward_workspace_bytes(C.byref(full))
+        self._fws = torch.empty(max(self._fws_bytes, 1), dtype=torch.uint8, device=dev)
+        if backward:
+            self._ws_bytes = self.lib.trifast_backward_workspace_bytes(C.byref(full))
+            self._ws = torch.empty(self._ws_bytes, dtype=torch.uint8, device=dev)
+            self.db_part = torch.empty((batch, heads, n, n), dtype=torch.float32, device=dev)
+            self.db_f32 = torch.empty((batch, heads, n, n), dtype=torch.float32, device=dev)
+            self.db = torch.empty((batch, heads, n, n), dtype=dtype, device=dev)
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        self.bytes_per_elem = es
+        self.kernel_launches = 0      # of the last run()
+
+    # -- views of the slot buffers for a block of r rows (always dense)
+    def _v5(self, name, slot, r):
+        return self._flat[name][slot][: self.batch * self.heads * r * self.n * self.d].view(
+            self.batch, self.heads, r, self.n, self.d)
+
+    def _vmask(self, slot, r):
+        return self._mask[slot][: self.batch * r * self.n].view(self.batch, r, self.n)
+
+    def _vlse(self, slot, r):
+        return self._lse[slot][: self.batch * self.heads * r * self.n]
+
+    def _copy_rows(self, dst5, src5, r0, r1, to_host):
+        """One asynchronous copy per (batch, head): each is a dense block on both sides."""
+        for b in range(self.batch):
+            for h in range(self.heads):
+                if to_host:
+                    dst5[b, h, r0:r1].copy_(src5[b, h], non_blocking=True)
+                else:
+                    dst5[b, h].copy_(src5[b, h, r0:r1], non_blocking=True)
+
+    def run(self, q, k, v, bias, mask, do=None, out=None, group=None):
+        """q, k, v (and do): pinned (batch, heads, rows, n, d); bias: pinned
+        (batch, heads, n, n); mask: pinned bool (batch, rows, n).  ``out`` is a dict
+        of pinned result tensors ``o`` (and ``dq, dk, dv, db``), allocated when
+        absent.  Everything is enqueued; the calling stream waits for the last
+        copy, so ``torch.cuda.current_stream().synchronize()`` (or an event on it)
+        marks the results complete.  Under ``group`` the db of all ranks' rows is
+        summed before it is copied back.
+        """
+        B, H, R, n, d = self.batch, self.heads, self.rows, self.n, self.d
+        bwd = self.backward
+        if bwd and do is None:
+            raise ValueError("this pipeline was built with backward=True: pass do")
+        shape5 = (B, H, R, n, d)
+        for nm, t in (("q", q), ("k", k), ("v", v)) + ((("do", do),) if bwd else ()):
+            _check_host5(nm, t, shape5, self.dtype)
+        if tuple(bias.shape) != (B, H, n, n) or bias.dtype != self.dtype or not bias.is_pinned() \
+                or not bias.is_contiguous():
+            raise ValueError("bias must be a pinned, contiguous (batch, heads, n, n) host tensor")
+        if tuple(mask.shape) != (B, R, n) or mask.dtype != torch.bool or not mask.is_pinned() \
+                or not mask.is_contiguous():
+            raise ValueError("mask must be a pinned, contiguous bool (batch, rows, n) host tensor")
+        m8 = mask.view(torch.uint8)
+        if out is None:
+            out = {}
+        for nm in (_NAMES_OUT if bwd else ("o",)):
+            if nm not in out:
+                out[nm] = torch.empty(shape5, dtype=self.dtype).pin_memory()
+            _check_host5(nm, out[nm], shape5, self.dtype)
+        if bwd and "db" not in out:
+            out["db"] = torch.empty((B, H, n, n), dtype=self.dtype).pin_memory()
+        src = dict(q=q, k=k, v=v, do=do)
+
+        lib, L = self.lib, _lib
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(cur)
+        run_stream = C.c_void_p(self.s_run.cuda_stream)
+        nchunks = (R + self.chunk - 1) // self.chunk
+        ev_in = [None] * nchunks
+        ev_run = [None] * nchunks
+        ev_out = [None] * nchunks
+        launches = 0
+
+        with torch.cuda.device(self.device):
+            with torch.cuda.stream(self.s_in):
+                self.bias.copy_(bias, non_blocking=True)
+            ab = L.t4(self.bias)
+            for c in range(nchunks):
+                slot = c % self.slots
+                r0, r1 = c * self.chunk, min(R, (c + 1) * self.chunk)
+                r = r1 - r0
+                # ---- host -> device
+                with torch.cuda.stream(self.s_in):
+                    if c >= self.slots:
+                        self.s_in.wait_event(ev_run[c - self.slots])   # inputs of the slot consumed
+                    for nm in (_NAMES_IN if bwd else ("q", "k", "v")):
+                        self._copy_rows(self._v5(nm, slot, r), src[nm], r0, r1, to_host=False)
+                    for b in range(B):
+                        self._vmask(slot, r)[b].copy_(m8[b, r0:r1], non_blocking=True)
+                    ev_in[c] = self.s_in.record_event()
+                # ---- kernels
+                with torch.cuda.stream(self.s_run):
+                    self.s_run.wait_event(ev_in[c])
+                    if c >= self.slots:
+                        self.s_run.wait_event(ev_out[c - self.slots])  # results of the slot copied out
+                    shp = L.make_shape(B, H, n, r, d, self.dtype)
+                    a = {nm: L.t5(self._v5(nm, slot, r)) for nm in self._flat}
+                    am = L.mask_view(self._vmask(slot, r))
+                    lse = C.c_void_p(self._vlse(slot, r).data_ptr())
+                    rc = lib.trifast_forward(C.byref(shp), C.byref(a["q"]), C.byref(a["k"]),
+                                             C.byref(a["v"]), C.byref(ab), C.byref(am),
+                                             C.byref(a["o"]), lse,
+                                             C.c_void_p(self._fws.data_ptr()),
+                                             C.c_size_t(self._fws_bytes), run_stream)
+                    L.check(rc, "trifast_forward")
+                    plan = L.pick_plan(B, H, n, r, d, self.dtype)
+                    tc = plan["kernel"] == L.KERNEL_TCGEN05
+                    launches += 1 + (2 if self._fws_bytes else 0)
+                    if bwd:
+                        part = self.db_f32 if c == 0 else self.db_part
+                        ws, wsb = C.c_void_p(self._ws.data_ptr()), C.c_size_t(self._ws_bytes)
+                        rc = lib.trifast_backward_db(
+                            C.byref(shp), C.byref(a["do"]), C.byref(a["q"]), C.byref(a["k"]),
+                            C.byref(a["v"]), C.byref(ab), C.byref(am), C.byref(a["o"]), lse,
+                            C.c_void_p(part.data_ptr()), ws, wsb, run_stream)
+                        L.check(rc, "trifast_backward_db")
+                        if c > 0:
+                            self.db_f32.add_(self.db_part)
+                        rc = lib.trifast_backward_dqkv(
+                            C.byref(shp), C.byref(a["do"]), C.byref(a["q"]), C.byref(a["k"]),
+                            C.byref(a["v"]), C.byref(ab), C.byref(am), lse, C.byref(a["dq"]),
+                            C.byref(a["dk"]), C.byref(a["dv"]), ws, wsb, run_stream)
+                        L.check(rc, "trifast_backward_dqkv")
+                        # row flags, bias copies, delta, db (+ split reduce), dq, dk/dv
+                        launches += 1 + (1 if tc else 0) + (1 if tc and n % 8 else 0) + 2 + \
+                            (1 if plan["db_row_splits"] > 1 else 0) + 2
+                    ev_run[c] = self.s_run.record_event()
+                # ---- device -> host
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(ev_run[c])
+                    for nm in (_NAMES_OUT if bwd else ("o",)):
+                        self._copy_rows(out[nm], self._v5(nm, slot, r), r0, r1, to_host=True)
+                    ev_out[c] = self.s_out.record_event()
+            if bwd:
+                with torch.cuda.stream(self.s_run):
+                    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+                        dist.all_reduce(self.db_f32, op=dist.ReduceOp.SUM, group=group)
+                    shp = L.make_shape(B, H, n, n, d, self.dtype)
+                    rc = lib.trifast_db_finalize(C.byref(shp), C.c_void_p(self.db_f32.data_ptr()),
+                                                 C.byref(L.t4(self.db)), run_stream)
+                    L.check(rc, "trifast_db_finalize")
+                    launches += 1
+                    ev_db = self.s_run.record_event()
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(ev_db)
+                    out["db"].copy_(self.db, non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_run)
+        cur.wait_stream(self.s_in)
+        self.kernel_launches = launches
+        return out
+
+
+def triangle_attention_host(q, k, v, bias, mask, do=None, device=None, chunk_rows: int = 64,
+                            out=None):
+    """One-shot form of :class:`HostPipeline` on a single GPU: pinned host tensors
+    in, pinned host tensors out (``{"o": ...}`` or, with ``do``, also ``dq, dk, dv,
+    db``).  Blocks until the results are in host memory."""
+    B, H, R, n, d = q.shape
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    pipe = HostPipeline(B, H, n, d, q.dtype, device, rows=R, chunk_rows=chunk_rows,
+                        backward=do is not None)
+    res = pipe.run(q, k, v, bias, mask, do=do, out=out)
+    torch.cuda.current_stream(device).synchronize()
+    return res
