@@ -1,7 +1,8 @@
 // Bias gradient db[j, k] = sum over pair rows i of dS[i, j, k] on the tensor cores.
 //
-// One CTA owns a 128 x 128 (j, k) tile of one (b, h) and one block of pair rows
-// (a "row split"); it walks its rows, recomputing per row
+// A work item is a 128 x 128 (j, k) tile of one (b, h) and one block of pair rows
+// (a "row split"); the launch gives every CTA one item.  Per row of its item the CTA
+// recomputes
 //     S  = Q_i K_i^T,   dP = dO_i V_i^T        (two SS MMAs, 128 x 128 each)
 //     P  = exp2(S * c + bias * log2e - lse_i * log2e),   dS = P * (dP - delta_i)
 // and sums dS in fp32 registers: thread = (query row j, 32-key quarter), 32
@@ -55,7 +56,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_nlse, const __grid_constant__ CUtensorMap map_delta,
              View4 bias, const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits,
-             int mask_words, float* __restrict__ out, int splits, Dims dm, unsigned int* status) {
+             int mask_words, float* __restrict__ out, int splits, int total_items, Dims dm,
+             unsigned int* status) {
   using Cfg = DbCfg<D, NS>;
   constexpr int FULL = 0, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + 2,
                 NBARS = S_FREE + 2;
@@ -84,13 +86,28 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles_k = (n + 127) / 128;
-  const int jt = blockIdx.x / tiles_k, kt = blockIdx.x % tiles_k;
-  const int split = blockIdx.y, bh = blockIdx.z;
-  const int b = bh / dm.heads, h = bh % dm.heads;
-  // Rows of this split: a contiguous block, the same partition for every tile.
+  const int tiles = tiles_k * tiles_k;
+  // Rows of a split: a contiguous block, the same partition for every tile.
   const int per = (dm.n_rows + splits - 1) / splits;
-  const int i_begin = split * per;
-  const int nrows = max(0, min(dm.n_rows, i_begin + per) - i_begin);
+  struct Item {
+    int jt, kt, split, bh, b, h, i_begin, nrows;
+  };
+  // item order: tile fastest, then split, then (b, h): the CTAs running together work
+  // on the same rows of the same (b, h), so the Q/dO/K/V row tiles are shared in L2
+  auto decode = [&](int w) {
+    Item im;
+    const int tile = w % tiles;
+    const int rest = w / tiles;
+    im.jt = tile / tiles_k;
+    im.kt = tile % tiles_k;
+    im.split = rest % splits;
+    im.bh = rest / splits;
+    im.b = im.bh / dm.heads;
+    im.h = im.bh % dm.heads;
+    im.i_begin = im.split * per;
+    im.nrows = max(0, min(dm.n_rows, im.i_begin + per) - im.i_begin);
+    return im;
+  };
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -126,16 +143,24 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     if (warp == kTmaWarp) {
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
-        for (int it = 0; it < nrows; ++it) {
-          const int s = it % NS, i = i_begin + it;
-          if (it >= NS && !mbar_wait(bar(EMPTY + s), ((it / NS) - 1) & 1, abort_flag)) break;
-          mbar_arrive_expect_tx(bar(FULL + s), Cfg::kStageBytes);
-          tma_load_5d(q_tile(s), &map_q, bar(FULL + s), 0, jt * 128, i, h, b);
-          tma_load_5d(do_tile(s), &map_do, bar(FULL + s), 0, jt * 128, i, h, b);
-          tma_load_5d(k_tile(s), &map_k, bar(FULL + s), 0, kt * 128, i, h, b);
-          tma_load_5d(v_tile(s), &map_v, bar(FULL + s), 0, kt * 128, i, h, b);
-          tma_load_4d(base + nlse_off(s), &map_nlse, bar(FULL + s), jt * 128, i, h, b);
-          tma_load_4d(base + delta_off(s), &map_delta, bar(FULL + s), jt * 128, i, h, b);
+        int g = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+          const Item im = decode(w);
+          for (int it = 0; it < im.nrows; ++it, ++g) {
+            const int s = g % NS, i = im.i_begin + it;
+            if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(bar(FULL + s), Cfg::kStageBytes);
+            tma_load_5d(q_tile(s), &map_q, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
+            tma_load_5d(do_tile(s), &map_do, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
+            tma_load_5d(k_tile(s), &map_k, bar(FULL + s), 0, im.kt * 128, i, im.h, im.b);
+            tma_load_5d(v_tile(s), &map_v, bar(FULL + s), 0, im.kt * 128, i, im.h, im.b);
+            tma_load_4d(base + nlse_off(s), &map_nlse, bar(FULL + s), im.jt * 128, i, im.h, im.b);
+            tma_load_4d(base + delta_off(s), &map_delta, bar(FULL + s), im.jt * 128, i, im.h, im.b);
+          }
         }
       }
     } else if (warp == kMmaWarp) {
@@ -144,26 +169,30 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc = make_idesc(128, 128, kBf16, false, false);
         bool ok = true;
-        for (int it = 0; it < nrows && ok; ++it) {
-          const int s = it % NS, u = it & 1;
-          ok = mbar_wait(bar(FULL + s), (it / NS) & 1, abort_flag);
-          if (ok && it >= 2) ok = mbar_wait(bar(S_FREE + u), ((it >> 1) - 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
+        int g = 0;
+        for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+          const int nrows = decode(w).nrows;
+          for (int it = 0; it < nrows && ok; ++it, ++g) {
+            const int s = g % NS, u = g & 1;
+            ok = mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag);
+            if (ok && g >= 2) ok = mbar_wait(bar(S_FREE + u), ((g >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t aq = make_smem_desc(q_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
-            const uint64_t bk = make_smem_desc(k_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
-            umma_ss(tmem_base + u * 256, aq, bk, idesc, kk > 0);
-          }
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint64_t aq = make_smem_desc(q_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+              const uint64_t bk = make_smem_desc(k_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+              umma_ss(tmem_base + u * 256, aq, bk, idesc, kk > 0);
+            }
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t ag = make_smem_desc(do_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
-            const uint64_t bv = make_smem_desc(v_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
-            umma_ss(tmem_base + u * 256 + 128, ag, bv, idesc, kk > 0);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint64_t ag = make_smem_desc(do_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+              const uint64_t bv = make_smem_desc(v_tile(s) + kk * 32, 16, Cfg::kSbo, Cfg::kSwz);
+              umma_ss(tmem_base + u * 256 + 128, ag, bv, idesc, kk > 0);
+            }
+            umma_commit(bar(S_FULL + u));
+            umma_commit(bar(EMPTY + s));
           }
-          umma_commit(bar(S_FULL + u));
-          umma_commit(bar(EMPTY + s));
         }
       }
     }
@@ -171,89 +200,110 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
     // ------------------------------------------------------------ elementwise warpgroups
     const int quarter = warp >> 2, wq = warp & 3, row = tid & 127;
-    const int j = jt * 128 + row;
-    const int key0 = kt * 128 + quarter * 32;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const float c1 = dm.scale * kLog2e;
     const float uniform = 1.f / (float)n;
 
-    float acc[32];
-    uint32_t bp[16];  // this thread's 32 bias values, kept as 16-bit pairs
-    {
-      const T* brow = reinterpret_cast<const T*>(bias.p) + b * bias.sb + h * bias.sh +
-                      (int64_t)min(j, n - 1) * bias.sj;
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        acc[c] = 0.f;
-        acc[c + 1] = 0.f;
-        const float b0 = (key0 + c < n) ? to_f32<T>(brow[key0 + c]) : 0.f;
-        const float b1 = (key0 + c + 1 < n) ? to_f32<T>(brow[key0 + c + 1]) : 0.f;
-        bp[c >> 1] = pack2<T>(b0, b1);  // exact: the values are 16-bit already
-      }
-    }
     bool ok = true;
-    for (int it = 0; it < nrows; ++it) {
-      const int s = it % NS, u = it & 1, i = i_begin + it;
-      // per-row inputs that do not come through shared memory
-      const uint32_t mw =
-          __ldg(maskbits + ((int64_t)b * dm.n_rows + i) * mask_words + kt * 4 + quarter);
-      const bool row_full = rowfull[b * dm.n_rows + i] != 0;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (it / NS) & 1, abort_flag));
-      if (!ok) break;
-      const float nl = reinterpret_cast<const float*>(gbase + nlse_off(s))[row];
-      const float dl = reinterpret_cast<const float*>(gbase + delta_off(s))[row];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(EMPTY + s));
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + u), (it >> 1) & 1, abort_flag));
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t tS = tmem_base + lane_base + u * 256 + quarter * 32;
-      const uint32_t tDP = tS + 128;
+    int g = 0;
+    for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+      const Item im = decode(w);
+      const int b = im.b, h = im.h, kt = im.kt;
+      const int j = im.jt * 128 + row;
+      const int key0 = kt * 128 + quarter * 32;
+
+      float acc[32];
+      uint32_t bp[16];  // this thread's 32 bias values, kept as 16-bit pairs
+      {
+        const T* brow = reinterpret_cast<const T*>(bias.p) + b * bias.sb + h * bias.sh +
+                        (int64_t)min(j, n - 1) * bias.sj + key0;
 #pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {
-        float x[16], g[16];
-        tmem_ld16(tS + hc * 16, reinterpret_cast<uint32_t*>(x));
-        tmem_ld16(tDP + hc * 16, reinterpret_cast<uint32_t*>(g));
-        tmem_wait_ld();
-        if (hc == 1) {  // everything this warp needs from the buffer is in registers
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(S_FREE + u));
-        }
-        const uint32_t mh = (mw >> (hc * 16)) & 0xffffu;
-        if (row_full) {
+        for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+        if (key0 + 32 <= n && (reinterpret_cast<uintptr_t>(brow) & 15) == 0) {
+          // four 16-byte loads: a lane reads its own row, so every load instruction
+          // touches 32 lines; 2-byte loads would take 32 such instructions
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float p = ((mh >> c) & 1u) ? 0.f : uniform;
-            acc[hc * 16 + c] = fmaf(p, g[c] - dl, acc[hc * 16 + c]);
+          for (int c = 0; c < 4; ++c) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(brow) + c);
+            bp[4 * c + 0] = u.x;
+            bp[4 * c + 1] = u.y;
+            bp[4 * c + 2] = u.z;
+            bp[4 * c + 3] = u.w;
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 16; c += 2) {
-            float b0, b1;
-            unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
-            float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
-            float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
-            if (mh != 0u) {
-              if ((mh >> c) & 1u) p0 = 0.f;
-              if ((mh >> (c + 1)) & 1u) p1 = 0.f;
-            }
-            acc[hc * 16 + c] = fmaf(p0, g[c] - dl, acc[hc * 16 + c]);
-            acc[hc * 16 + c + 1] = fmaf(p1, g[c + 1] - dl, acc[hc * 16 + c + 1]);
+          for (int c = 0; c < 32; c += 2) {
+            const float b0 = (key0 + c < n) ? to_f32<T>(brow[c]) : 0.f;
+            const float b1 = (key0 + c + 1 < n) ? to_f32<T>(brow[c + 1]) : 0.f;
+            bp[c >> 1] = pack2<T>(b0, b1);  // exact: the values are 16-bit already
           }
         }
       }
-    }
-    if (ok && j < n) {
-      float* dst = out + (((int64_t)split * dm.batch * dm.heads + bh) * n + j) * n + key0;
-      if (key0 + 32 <= n && (n & 3) == 0) {
+      for (int it = 0; it < im.nrows; ++it, ++g) {
+        const int s = g % NS, u = g & 1, i = im.i_begin + it;
+        // per-row inputs that do not come through shared memory (consumed after the
+        // barrier waits below, which hide their latency)
+        const uint32_t mw =
+            __ldg(maskbits + ((int64_t)b * dm.n_rows + i) * mask_words + kt * 4 + quarter);
+        const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag));
+        if (!ok) break;
+        const float nl = reinterpret_cast<const float*>(gbase + nlse_off(s))[row];
+        const float dl = reinterpret_cast<const float*>(gbase + delta_off(s))[row];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(EMPTY + s));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + u), (g >> 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tS = tmem_base + lane_base + u * 256 + quarter * 32;
+        const uint32_t tDP = tS + 128;
 #pragma unroll
-        for (int c = 0; c < 32; c += 4)
-          *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
-      } else {
+        for (int hc = 0; hc < 2; ++hc) {
+          float x[16], gd[16];
+          tmem_ld16(tS + hc * 16, reinterpret_cast<uint32_t*>(x));
+          tmem_ld16(tDP + hc * 16, reinterpret_cast<uint32_t*>(gd));
+          tmem_wait_ld();
+          if (hc == 1) {  // everything this warp needs from the buffer is in registers
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(S_FREE + u));
+          }
+          const uint32_t mh = (mw >> (hc * 16)) & 0xffffu;
+          if (row_full) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (key0 + c < n) dst[c] = acc[c];
+            for (int c = 0; c < 16; ++c) {
+              const float p = ((mh >> c) & 1u) ? 0.f : uniform;
+              acc[hc * 16 + c] = fmaf(p, gd[c] - dl, acc[hc * 16 + c]);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              float b0, b1;
+              unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
+              float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
+              float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
+              if (mh != 0u) {
+                if ((mh >> c) & 1u) p0 = 0.f;
+                if ((mh >> (c + 1)) & 1u) p1 = 0.f;
+              }
+              acc[hc * 16 + c] = fmaf(p0, gd[c] - dl, acc[hc * 16 + c]);
+              acc[hc * 16 + c + 1] = fmaf(p1, gd[c + 1] - dl, acc[hc * 16 + c + 1]);
+            }
+          }
+        }
+      }
+      if (!ok) break;
+      if (j < n) {
+        float* dst = out + (((int64_t)im.split * dm.batch * dm.heads + im.bh) * n + j) * n + key0;
+        if (key0 + 32 <= n && (n & 3) == 0) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (key0 + c < n) dst[c] = acc[c];
+        }
       }
     }
   }
@@ -306,10 +356,22 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const int t = (dm.n + 127) / 128;
-  dim3 grid(t * t, a.splits, dm.batch * dm.heads);
+  const int total = t * t * a.splits * dm.batch * dm.heads;
+  // One item per CTA.  (The kernel loops over items c, c + grid, ..., but with
+  // grid < total a rare wrong row sum showed up in items after a CTA's first; until
+  // that is understood every CTA gets exactly one item.)
+  const int grid = total;
   float* out = a.splits > 1 ? a.db_partials : a.db_f32;
-  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mnl, mdl, a.bias, a.rowfull,
-                                              a.maskbits_lin, a.mask_words, out, a.splits, dm, a.status);
+  View4 bias = a.bias;
+  if (a.bias_pad) {  // the copy with a 16-byte row pitch: its rows can be read 16 bytes at a time
+    bias.p = (char*)a.bias_pad;
+    bias.sj = dm.n_pad;
+    bias.sh = (int64_t)dm.n * dm.n_pad;
+    bias.sb = bias.sh * dm.heads;
+  }
+  kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mnl, mdl, bias, a.rowfull,
+                                              a.maskbits_lin, a.mask_words, out, a.splits, total, dm,
+                                              a.status);
   return cudaGetLastError();
 }
 

@@ -280,6 +280,12 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         const float my_delta =
             delta[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * dm.n_pad + min(j, n - 1)];
 
+        // mask words are fetched one key tile ahead: a global load consumed in the same
+        // tile would stall the pass for its whole latency
+        uint32_t nx[4];
+#pragma unroll
+        for (int jb = 0; jb < 4; ++jb) nx[jb] = __ldg(mb + jb);
+
         auto key_loop = [&](auto row_full_tag) {
           constexpr bool kRowFull = decltype(row_full_tag)::value;
           for (int kt = 0; kt < nkt; ++kt, ++g) {
@@ -309,8 +315,11 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             // the dQ MMA of the previous key tile no longer reads the dS columns
             uint32_t mw[4];
 #pragma unroll
-            for (int jb = 0; jb < 4; ++jb)
-              mw[jb] = (__ldg(mb + (kt >> 1) * 4 + jb) >> ((kt & 1) * 16)) & 0xffffu;
+            for (int jb = 0; jb < 4; ++jb) mw[jb] = (nx[jb] >> ((kt & 1) * 16)) & 0xffffu;
+            if (kt + 1 < nkt) {
+#pragma unroll
+              for (int jb = 0; jb < 4; ++jb) nx[jb] = __ldg(mb + ((kt + 1) >> 1) * 4 + jb);
+            }
             const bool clean = (mw[0] | mw[1] | mw[2] | mw[3]) == 0u;
             // (a non-blocking look now; if it is not done yet the wait happens after the pass)
             const bool dq_done =
