@@ -76,8 +76,8 @@ struct FwdCfg {
   static constexpr int kThreads = R * 128 + 128;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
-  // per softmax warp: 4 mask words per 128-key chunk
-  static int mask_bytes(int n) { return 4 * R * ((n + kBK - 1) / kBK) * 16; }
+  // per softmax warp: 4 mask words per 128-key chunk, two buffers (this item's and the next's)
+  static int mask_bytes(int n) { return 2 * 4 * R * ((n + kBK - 1) / kBK) * 16; }
   static int smem_bytes(int n) {
     const int head = (kHeaderBytes + mask_bytes(n) + 1023) / 1024 * 1024;
     return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
@@ -110,11 +110,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint8_t* gbase = smem_raw + (base - raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
-  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][nkt][4]
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][2][nkt][4]
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
-  const uint32_t tiles_off = (kHeaderBytes + 4 * R * nkt * 16 + 1023u) & ~1023u;
+  const uint32_t tiles_off = (kHeaderBytes + 2 * 4 * R * nkt * 16 + 1023u) & ~1023u;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kTileBytes; };
@@ -278,43 +278,69 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + r * 256;
     const uint32_t tP = tS + 128, tO = tS + 192;
-    uint32_t* mb = maskbits + warp * nkt * 4;  // this warp's own copy: no cross-warp sync
+    uint32_t* mb = maskbits + warp * 2 * nkt * 4;  // this warp's own two copies: no cross-warp sync
+
+    // Key mask of a row as bit words (bit set = key dropped or beyond n), made one item
+    // ahead so that the loads run under the last PV of the current item.  Lane l reads
+    // keys 4l .. 4l+3 of a 128-key chunk as one word; word j of the chunk then holds,
+    // at bit l, key 4l + j.
+    struct RowMask {
+      const uint32_t* words;
+      bool full;
+    };
+    auto row_mask = [&](int w, uint32_t* dst) -> RowMask {
+      const Item im = decode(w);
+      const int i = slot_row(im, r), b = im.b;
+      RowMask rm;
+      if (ws_maskbits != nullptr) {
+        // made by the prepare step (n % 8 != 0: the mask rows are not word-aligned)
+        rm.words = ws_maskbits + ((int64_t)b * dm.n_rows + i) * ws_mask_words;
+        rm.full = ws_rowfull[b * dm.n_rows + i] != 0;
+        return rm;
+      }
+      const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+      uint32_t open = 0;
+      // four chunks at a time: the loads go out together, so a batch costs one
+      // memory latency instead of four
+      for (int c0 = 0; c0 < nkt; c0 += 4) {
+        uint32_t u[4];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int key4 = (c0 + cc) * kBK + 4 * lane;
+          u[cc] = (c0 + cc < nkt && key4 < n) ? __ldg(reinterpret_cast<const uint32_t*>(mrow + key4))
+                                              : 0x01010101u;
+        }
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int c = c0 + cc;
+          if (c < nkt) {
+            const uint32_t vm = __ballot_sync(0xffffffffu, c * kBK + 4 * lane < n);
+#pragma unroll
+            for (int jb = 0; jb < 4; ++jb) {
+              const uint32_t bits = __ballot_sync(0xffffffffu, ((u[cc] >> (8 * jb)) & 0xffu) != 0u);
+              if (lane == 0) dst[c * 4 + jb] = bits;
+              open |= ~bits & vm;
+            }
+          }
+        }
+      }
+      __syncwarp();
+      rm.words = dst;
+      rm.full = open == 0u;
+      return rm;
+    };
 
     int g = 0, it = 0;
     bool ok = true;
+    RowMask next_mask{mb, false};
+    if ((int)blockIdx.x < items.total) next_mask = row_mask(blockIdx.x, mb);
     for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
       const Item im = decode(w);
       const int i = slot_row(im, r);
       const bool do_store = im.i0 + r < dm.n_rows;
       const int b = im.b, h = im.h, jt = im.jt;
-
-      // Key mask of row i as bit words (bit set = key dropped or beyond n).  Lane l
-      // reads keys 4l .. 4l+3 of a 128-key chunk as one word; word j of the chunk
-      // then holds, at bit l, key 4l + j.
-      bool row_full;
-      const uint32_t* mbr = mb;  // where this row's mask words are read from
-      if (ws_maskbits != nullptr) {
-        // made by the prepare step (n % 8 != 0: the mask rows are not word-aligned)
-        mbr = ws_maskbits + ((int64_t)b * dm.n_rows + i) * ws_mask_words;
-        row_full = ws_rowfull[b * dm.n_rows + i] != 0;
-      } else {
-        const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
-        uint32_t open = 0;
-        for (int c = 0; c < nkt; ++c) {
-          const int key4 = c * kBK + 4 * lane;
-          const bool valid = key4 < n;
-          const uint32_t u = valid ? __ldg(reinterpret_cast<const uint32_t*>(mrow + key4)) : 0x01010101u;
-          const uint32_t vm = __ballot_sync(0xffffffffu, valid);
-#pragma unroll
-          for (int jb = 0; jb < 4; ++jb) {
-            const uint32_t bits = __ballot_sync(0xffffffffu, ((u >> (8 * jb)) & 0xffu) != 0u);
-            if (lane == 0) mb[c * 4 + jb] = bits;
-            open |= ~bits & vm;
-          }
-        }
-        __syncwarp();
-        row_full = open == 0u;
-      }
+      const bool row_full = next_mask.full;
+      const uint32_t* mbr = next_mask.words;
 
       float m_run = kMaxInit, l_run = 0.f;
       // The key loop exists in two copies, chosen once per row: the fully-masked-row
@@ -459,6 +485,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       };
       if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
       if (!ok) break;
+
+      // the next item's mask words, while the last PV of this item runs
+      if (w + (int)gridDim.x < items.total)
+        next_mask = row_mask(w + gridDim.x, mb + ((it + 1) & 1) * nkt * 4);
 
       // epilogue of the item: O / l and lse
       ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (g - 1) & 1, abort_flag));
