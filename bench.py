@@ -269,6 +269,23 @@ def time_events(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def time_events_each(fn, iters):
+    """Per-iteration device times (one event pair per call), for quantiles."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(iters)]
+    for e0, e1 in evs:
+        e0.record()
+        fn()
+        e1.record()
+    torch.cuda.synchronize()
+    return sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+
+
+def quantiles(xs):
+    pick = lambda f: xs[min(len(xs) - 1, int(f * len(xs)))]
+    return {"p10": pick(0.1), "p50": pick(0.5), "p90": pick(0.9)}
+
+
 def run_native(args, w):
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))
@@ -317,7 +334,9 @@ def run_native(args, w):
     from trifast_b200.host import HostPipeline
     host = [t.cpu().pin_memory() for t in (q, k, v, b, m, do)]
     bs_, h_, rows_, n_, d_ = q.shape
-    pipe = HostPipeline(bs_, h_, n_, d_, q.dtype, dev, rows=rows_, chunk_rows=args.e2e_chunk_rows,
+    # blocks small enough that a shard still has several of them in flight
+    chunk = max(8, min(args.e2e_chunk_rows, (rows_ + 3) // 4))
+    pipe = HostPipeline(bs_, h_, n_, d_, q.dtype, dev, rows=rows_, chunk_rows=chunk,
                         backward=w.backward)
     outs_host = None
     group = dist.group.WORLD if world > 1 else None
@@ -340,13 +359,19 @@ def run_native(args, w):
         e2e_ms = float(t)
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in outs_host.values())
+    if world > 1:   # bytes moved by the whole job, not by rank 0
+        t = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        h2d, d2h = int(t[0]), int(t[1])
     del host, outs_host, pipe
     total_flops = flops_step(w)
 
     # ---- per-phase timing, roofline and the CPU baseline (single GPU only) ------------
     phases, roofline, cpu = None, None, None
     peaks = measured_peaks()
+    step_q = None
     if world == 1:
+        step_q = quantiles(time_events_each(step.step, max(args.steps, 10)))
         phases = {"forward": time_events(step.forward, args.steps)}
         kernels_flops = {"forward": flops_fwd(w)}
         if w.backward:
@@ -402,6 +427,9 @@ def run_native(args, w):
         }
         if phases is not None:
             line["phases_ms"] = phases
+            line["ms_per_step_quantiles"] = step_q
+            line["forward_only"] = {"ms": phases["forward"],
+                                    "tflops": flops_fwd(w) / (phases["forward"] * 1e-3) / 1e12}
             line["roofline"] = roofline
         if cpu is not None:
             line["cpu_baseline"] = cpu

@@ -275,6 +275,16 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
               const float p = ((mh >> c) & 1u) ? 0.f : uniform;
               acc[hc * 16 + c] = fmaf(p, gd[c] - dl, acc[hc * 16 + c]);
             }
+          } else if (mh == 0u) {  // no dropped key: a straight block the compiler can overlap
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              float b0, b1;
+              unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
+              const float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
+              const float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
+              acc[hc * 16 + c] = fmaf(p0, gd[c] - dl, acc[hc * 16 + c]);
+              acc[hc * 16 + c + 1] = fmaf(p1, gd[c + 1] - dl, acc[hc * 16 + c + 1]);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
@@ -282,10 +292,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
               unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
               float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
               float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
-              if (mh != 0u) {
-                if ((mh >> c) & 1u) p0 = 0.f;
-                if ((mh >> (c + 1)) & 1u) p1 = 0.f;
-              }
+              p0 = ((mh >> c) & 1u) ? 0.f : p0;
+              p1 = ((mh >> (c + 1)) & 1u) ? 0.f : p1;
               acc[hc * 16 + c] = fmaf(p0, gd[c] - dl, acc[hc * 16 + c]);
               acc[hc * 16 + c + 1] = fmaf(p1, gd[c + 1] - dl, acc[hc * 16 + c + 1]);
             }

@@ -37,8 +37,6 @@ constexpr int kBJ = 128, kBK = 64;
 #endif
 constexpr bool kSlotToken = TRIFAST_DQ_TOKEN != 0;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kSmemLimit = 232448;
-constexpr int kHeaderBytes = 512;
 // Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
 // the math warpgroups gain must not exceed what the issue warpgroup releases, or
 // the request blocks forever.
@@ -330,38 +328,44 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             if (lane == 0) mbar_arrive(bar(S_FREE + r));
 
             // One fused pass per 8 keys: bias load and unpack (LSU, ALU), two FMAs, the
-            // exponential (MUFU), dS and the 16-bit pack.
+            // exponential (MUFU), dS and the 16-bit pack.  Two copies, chosen per tile:
+            // the copy for tiles without dropped keys has no branch in it, so the
+            // compiler can overlap the eight groups.
             uint32_t pk[32];
             const uint8_t* brow = gbase + bias_off(s) + t * 128;
+            auto pass = [&](auto clean_tag) {
+              constexpr bool kClean = decltype(clean_tag)::value;
 #pragma unroll
-            for (int q8 = 0; q8 < 8; ++q8) {
-              float p[8];
-              if (kRowFull) {
+              for (int q8 = 0; q8 < 8; ++q8) {
+                float p[8];
+                if (kRowFull) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) p[e] = uniform;
-              } else {
-                const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
-                float bv[8];
-                unpack2<T>(u.x, bv[0], bv[1]);
-                unpack2<T>(u.y, bv[2], bv[3]);
-                unpack2<T>(u.z, bv[4], bv[5]);
-                unpack2<T>(u.w, bv[6], bv[7]);
+                  for (int e = 0; e < 8; ++e) p[e] = uniform;
+                } else {
+                  const uint4 u = *reinterpret_cast<const uint4*>(brow + ((q8 ^ (t & 7)) << 4));
+                  float bv[8];
+                  unpack2<T>(u.x, bv[0], bv[1]);
+                  unpack2<T>(u.y, bv[2], bv[3]);
+                  unpack2<T>(u.z, bv[4], bv[5]);
+                  unpack2<T>(u.w, bv[6], bv[7]);
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, neg_lse2)));
-              }
-              if (!clean) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int c = q8 * 8 + e;
-                  if ((mw[c & 3] >> (c >> 2)) & 1u) p[e] = 0.f;
+                  for (int e = 0; e < 8; ++e)
+                    p[e] = ex2(fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, neg_lse2)));
                 }
-              }
+                if (!kClean) {
 #pragma unroll
-              for (int e = 0; e < 8; e += 2)
-                pk[(q8 * 8 + e) >> 1] = pack2<T>(p[e] * (gd[q8 * 8 + e] - my_delta),
-                                                 p[e + 1] * (gd[q8 * 8 + e + 1] - my_delta));
-            }
+                  for (int e = 0; e < 8; ++e) {
+                    const int c = q8 * 8 + e;
+                    p[e] = ((mw[c & 3] >> (c >> 2)) & 1u) ? 0.f : p[e];
+                  }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; e += 2)
+                  pk[(q8 * 8 + e) >> 1] = pack2<T>(p[e] * (gd[q8 * 8 + e] - my_delta),
+                                                   p[e + 1] * (gd[q8 * 8 + e + 1] - my_delta));
+              }
+            };
+            if (clean) pass(std::true_type{}); else pass(std::false_type{});
             __syncwarp();
             if (lane == 0) {
               mbar_arrive(bar(EMPTY + s));  // bias tile consumed by this warp
