@@ -69,8 +69,35 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc = index, None
+        self.thread, self.samples, self.halt = None, [], None
+
+    def _nvml_loop(self, pynvml, handle):
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x4: "sw_power_cap"}
+        mx = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        while not self.halt.is_set():
+            sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            try:
+                bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+            except AttributeError:
+                bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+            self.samples.append((sm, mx, [n for b, n in names.items() if bits & b]))
+            self.halt.wait(0.002)
 
     def start(self):
+        # in-process NVML reads every 2 ms (a timed region can be a few tens of ms long);
+        # the nvidia-smi loop is the fallback.  Both only read.
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.halt = threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
@@ -80,6 +107,14 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.halt.set()
+            self.thread.join(timeout=2)
+            sm = sorted(x[0] for x in self.samples)
+            reasons = sorted({r for x in self.samples for r in x[2]})
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                    "sm_max_mhz": self.samples[0][1] if self.samples else None,
+                    "reasons": reasons, "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         self.proc.terminate()

@@ -522,6 +522,38 @@ __global__ void db_reduce_kernel(const float* partials, float* out, int splits, 
   out[idx] = acc;
 }
 
+// four elements per thread (count % 4 == 0)
+__global__ void db_reduce4_kernel(const float4* partials, float4* out, int splits, int64_t count4) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count4) return;
+  float4 acc = __ldg(partials + idx);
+  for (int s = 1; s < splits; ++s) {  // fixed split order: deterministic
+    const float4 v = __ldg(partials + (int64_t)s * count4 + idx);
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
+  }
+  out[idx] = acc;
+}
+
+// four keys of one row per thread (n % 4 == 0, destination rows 8-byte aligned; T is 16 bits)
+template <typename T>
+__global__ void db_cast4_kernel(const float4* src, View4 db, int heads, int n, int64_t count4) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= count4) return;
+  const int n4 = n >> 2;
+  const int key = (int)(idx % n4) * 4;
+  int64_t r = idx / n4;
+  const int j = (int)(r % n);
+  r /= n;
+  const int h = (int)(r % heads), b = (int)(r / heads);
+  const float4 v = __ldg(src + idx);
+  T* dst = (T*)db.p + b * db.sb + h * db.sh + (int64_t)j * db.sj + key;
+  const T o4[4] = {from_f32<T>(v.x), from_f32<T>(v.y), from_f32<T>(v.z), from_f32<T>(v.w)};
+  *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o4);
+}
+
 template <typename T>
 __global__ void db_cast_kernel(const float* src, View4 db, int heads, int n, int64_t count) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -620,6 +652,13 @@ cudaError_t simt_bwd_db(const BwdArgs& a, cudaStream_t s) {
 cudaError_t db_reduce_splits(const BwdArgs& a, cudaStream_t s) {
   if (a.splits <= 1) return cudaSuccess;
   const int64_t count = (int64_t)a.dm.batch * a.dm.heads * a.dm.n * a.dm.n;
+  if (count % 4 == 0) {  // the partials and db_f32 sit on 256-byte boundaries of the workspace
+    const int64_t c4 = count / 4;
+    db_reduce4_kernel<<<(unsigned)((c4 + 255) / 256), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(a.db_partials), reinterpret_cast<float4*>(a.db_f32), a.splits,
+        c4);
+    return cudaGetLastError();
+  }
   db_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(a.db_partials, a.db_f32,
                                                                  a.splits, count);
   return cudaGetLastError();
@@ -652,6 +691,19 @@ cudaError_t simt_bwd_dkv(const BwdArgs& a, cudaStream_t s) {
 cudaError_t db_cast(const float* db_f32, View4 db, int dtype, int batch, int heads, int n,
                     cudaStream_t s) {
   const int64_t count = (int64_t)batch * heads * n * n;
+  const bool wide = dtype != TRIFAST_F32 && n % 4 == 0 && db.sj % 4 == 0 && db.sh % 4 == 0 &&
+                    db.sb % 4 == 0 && (reinterpret_cast<uintptr_t>(db.p) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(db_f32) & 15) == 0;
+  if (wide) {
+    const int64_t c4 = count / 4;
+    const unsigned blocks4 = (unsigned)((c4 + 255) / 256);
+    const float4* src = reinterpret_cast<const float4*>(db_f32);
+    if (dtype == TRIFAST_BF16)
+      db_cast4_kernel<__nv_bfloat16><<<blocks4, 256, 0, s>>>(src, db, heads, n, c4);
+    else
+      db_cast4_kernel<__half><<<blocks4, 256, 0, s>>>(src, db, heads, n, c4);
+    return cudaGetLastError();
+  }
   const unsigned blocks = (unsigned)((count + 255) / 256);
   switch (dtype) {
     case TRIFAST_F32: db_cast_kernel<float><<<blocks, 256, 0, s>>>(db_f32, db, heads, n, count); break;

@@ -261,13 +261,20 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
       int g = 0, it = 0;
       bool ok = true;
+      // The row flag picks the loop copy at the top of an item, so its load would be
+      // paid in full there: it is fetched one item ahead, under the previous epilogue.
+      auto row_flag = [&](int w) -> bool {
+        const Item im = decode(w);
+        return rowfull[im.b * dm.n_rows + slot_row(im, r)] != 0;
+      };
+      bool row_full_next = ((int)blockIdx.x < items.total) ? row_flag(blockIdx.x) : false;
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
         const Item im = decode(w);
         const int i = slot_row(im, r);
         const bool do_store = im.i0 + r < dm.n_rows;
         const int b = im.b, h = im.h;
         const int j = im.jt * kBJ + t;
-        const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+        const bool row_full = row_full_next;
 
         // Key mask of row i as packed words made by the prepare step (bit set = key
         // dropped or beyond n; none dropped inside n on a fully masked row).  Per 128-key
@@ -385,6 +392,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         };
         if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
         if (!ok) break;
+        if (w + (int)gridDim.x < items.total) row_full_next = row_flag(w + gridDim.x);
 
         ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));
         if (!ok) break;
