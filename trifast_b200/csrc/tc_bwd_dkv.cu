@@ -280,19 +280,19 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       // Row flag and this thread's mask byte pick the loop copy at the top of an item, so
       // their loads would be paid in full there: they are fetched one item ahead, under
       // the previous epilogue.
-      struct KeyState {
-        bool row_full, masked;
+      struct KeyState {  // raw bytes: compared at the top of their own item, not where they are loaded
+        uint32_t row_full, masked;
       };
       auto key_state = [&](int w) -> KeyState {
         const Item im = decode(w);
         const int i = slot_row(im, r);
         const int key = min(im.kt * kBKeys + t, n - 1);
         KeyState ks;
-        ks.row_full = rowfull[im.b * dm.n_rows + i] != 0;
-        ks.masked = mask.p[im.b * mask.sb + (int64_t)i * mask.si + key] != 0;
+        ks.row_full = rowfull[im.b * dm.n_rows + i];
+        ks.masked = mask.p[im.b * mask.sb + (int64_t)i * mask.si + key];
         return ks;
       };
-      KeyState next_state{false, false};
+      KeyState next_state{0u, 0u};
       if ((int)blockIdx.x < items.total) next_state = key_state(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
         const Item im = decode(w);
@@ -300,10 +300,10 @@ tc_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const bool do_store = im.i0 + r < dm.n_rows;
         const int b = im.b, h = im.h;
         const int key = im.kt * kBKeys + t;
-        const bool row_full = next_state.row_full;
+        const bool row_full = next_state.row_full != 0u;
         // weight of this thread's key: 0 when dropped (or beyond n); on a fully masked
         // row every key inside n weighs 1/n
-        const bool dropped = key >= n || (!row_full && next_state.masked);
+        const bool dropped = key >= n || (!row_full && next_state.masked != 0u);
         // The key weight pattern is fixed for the whole query loop, so the loop is
         // instantiated per pattern of this warp: 0 = every key kept (no selects),
         // 1 = mixed, 2 = every key dropped (no exponentials), 3 = fully masked row.

@@ -261,35 +261,52 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
 
       int g = 0, it = 0;
       bool ok = true;
-      // The row flag picks the loop copy at the top of an item, so its load would be
-      // paid in full there: it is fetched one item ahead, under the previous epilogue.
-      auto row_flag = [&](int w) -> bool {
-        const Item im = decode(w);
-        return rowfull[im.b * dm.n_rows + slot_row(im, r)] != 0;
+      // What an item needs from global memory before its first tile (row flag, this
+      // thread's lse and delta, the first mask words) is loaded one item ahead, before
+      // the wait of the previous epilogue, and only used (compared, scaled) at the top
+      // of its own item: a load that is used where it is issued stalls the warp for
+      // the whole memory latency.
+      struct ItemLoads {
+        uint32_t flag;
+        float lse, delta;
+        uint32_t nx[4];
       };
-      bool row_full_next = ((int)blockIdx.x < items.total) ? row_flag(blockIdx.x) : false;
+      auto item_loads = [&](int w) -> ItemLoads {
+        const Item im = decode(w);
+        const int i = slot_row(im, r);
+        const int64_t row = ((int64_t)im.b * dm.heads + im.h) * dm.n_rows + i;
+        const int jc = min(im.jt * kBJ + t, n - 1);
+        ItemLoads ld;
+        ld.flag = rowfull[im.b * dm.n_rows + i];
+        ld.lse = __ldg(lse + row * n + jc);
+        ld.delta = __ldg(delta + row * dm.n_pad + jc);
+        const uint32_t* mrow = maskbits + ((int64_t)im.b * dm.n_rows + i) * mask_words;
+#pragma unroll
+        for (int jb = 0; jb < 4; ++jb) ld.nx[jb] = __ldg(mrow + jb);
+        return ld;
+      };
+      ItemLoads next_loads{};
+      if ((int)blockIdx.x < items.total) next_loads = item_loads(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
         const Item im = decode(w);
         const int i = slot_row(im, r);
         const bool do_store = im.i0 + r < dm.n_rows;
         const int b = im.b, h = im.h;
         const int j = im.jt * kBJ + t;
-        const bool row_full = row_full_next;
+        const bool row_full = next_loads.flag != 0u;
 
         // Key mask of row i as packed words made by the prepare step (bit set = key
         // dropped or beyond n; none dropped inside n on a fully masked row).  Per 128-key
         // chunk c: word c*4 + jb holds, at bit l, key c*128 + 4*l + jb.
         const uint32_t* mb = maskbits + ((int64_t)b * dm.n_rows + i) * mask_words;
-        const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + min(j, n - 1);
-        const float neg_lse2 = -lse[stat] * kLog2e;
-        const float my_delta =
-            delta[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * dm.n_pad + min(j, n - 1)];
+        const float neg_lse2 = -next_loads.lse * kLog2e;
+        const float my_delta = next_loads.delta;
 
         // mask words are fetched one key tile ahead: a global load consumed in the same
         // tile would stall the pass for its whole latency
         uint32_t nx[4];
 #pragma unroll
-        for (int jb = 0; jb < 4; ++jb) nx[jb] = __ldg(mb + jb);
+        for (int jb = 0; jb < 4; ++jb) nx[jb] = next_loads.nx[jb];
 
         auto key_loop = [&](auto row_full_tag) {
           constexpr bool kRowFull = decltype(row_full_tag)::value;
@@ -392,7 +409,7 @@ tc_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         };
         if (row_full) key_loop(std::true_type{}); else key_loop(std::false_type{});
         if (!ok) break;
-        if (w + (int)gridDim.x < items.total) row_full_next = row_flag(w + gridDim.x);
+        if (w + (int)gridDim.x < items.total) next_loads = item_loads(w + gridDim.x);
 
         ok = __all_sync(0xffffffffu, mbar_wait(bar(DQ_DONE + r), (g - 1) & 1, abort_flag));
         if (!ok) break;
