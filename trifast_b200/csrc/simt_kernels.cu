@@ -171,21 +171,41 @@ __global__ void delta_kernel(View5 o, View5 d_o, const float* lse, float* delta,
 }
 
 // bias_t[b, h, k, j] = bias[b, h, j, k] (row pitch n_pad) for 2-byte elements (the dk/dv kernel reads
-// the bias with keys on the rows).
-__global__ void bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int n, int n_pad) {
-  __shared__ uint16_t tile[32][33];
+// the bias with keys on the rows).  64 x 64 tiles; 4-byte accesses on both sides when the rows allow it.
+__global__ void __launch_bounds__(256)
+bias_transpose_kernel(View4 bias, uint16_t* out, int heads, int n, int n_pad) {
+  __shared__ uint16_t tile[64][66];
   const int bh = blockIdx.z, b = bh / heads, h = bh % heads;
   const uint16_t* src = (const uint16_t*)bias.p + b * bias.sb + h * bias.sh;
   uint16_t* dst = out + (int64_t)bh * n * n_pad;
-  const int j0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
-  for (int r = threadIdx.y; r < 32; r += 8) {
-    const int j = j0 + r, k = k0 + threadIdx.x;
-    if (j < n && k < n) tile[r][threadIdx.x] = src[(int64_t)j * bias.sj + k];
+  const int j0 = blockIdx.y * 64, k0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const bool pairs_in = (bias.sj % 2 == 0) && (bias.sh % 2 == 0) && (bias.sb % 2 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(bias.p) & 3) == 0);
+  for (int r = ty; r < 64; r += 8) {
+    const int j = j0 + r, k = k0 + 2 * tx;
+    if (j < n) {
+      if (pairs_in && k + 1 < n) {
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(src + (int64_t)j * bias.sj + k);
+        tile[r][2 * tx] = (uint16_t)(u & 0xffffu);
+        tile[r][2 * tx + 1] = (uint16_t)(u >> 16);
+      } else {
+        if (k < n) tile[r][2 * tx] = src[(int64_t)j * bias.sj + k];
+        if (k + 1 < n) tile[r][2 * tx + 1] = src[(int64_t)j * bias.sj + k + 1];
+      }
+    }
   }
   __syncthreads();
-  for (int r = threadIdx.y; r < 32; r += 8) {
-    const int k = k0 + r, j = j0 + threadIdx.x;
-    if (j < n && k < n) dst[(int64_t)k * n_pad + j] = tile[threadIdx.x][r];
+  for (int r = ty; r < 64; r += 8) {  // output row k0 + r holds queries j0 .. j0 + 63
+    const int k = k0 + r, j = j0 + 2 * tx;
+    if (k < n) {
+      if (j + 1 < n) {  // n_pad is even and dst 4-byte aligned: a pair never straddles
+        const uint32_t u = (uint32_t)tile[2 * tx][r] | ((uint32_t)tile[2 * tx + 1][r] << 16);
+        *reinterpret_cast<uint32_t*>(dst + (int64_t)k * n_pad + j) = u;
+      } else if (j < n) {
+        dst[(int64_t)k * n_pad + j] = tile[2 * tx][r];
+      }
+    }
   }
 }
 
@@ -608,8 +628,8 @@ cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
                                                       a.maskbits_lin, a.mask_words);
   if (a.bias_t) {
-    dim3 grid((dm.n + 31) / 32, (dm.n + 31) / 32, dm.batch * dm.heads);
-    bias_transpose_kernel<<<grid, dim3(32, 8), 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n,
+    dim3 grid((dm.n + 63) / 64, (dm.n + 63) / 64, dm.batch * dm.heads);
+    bias_transpose_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n,
                                                        dm.n_pad);
   }
   if (a.bias_pad) {
