@@ -50,7 +50,19 @@ def _worker(rank, world, port, n, dtype, out):
                 torch.equal(kl.grad, kw.grad[:, :, rows]), torch.equal(vl.grad, vw.grad[:, :, rows])]
         db_err = float((bl.grad.float() - bw.grad.float()).abs().max() /
                        bw.grad.float().abs().max())
-        out.put((rank, same, db_err))
+        # the same shard through the host-resident pipeline (pinned host tensors, db summed
+        # over the ranks inside run())
+        from trifast_b200.host import HostPipeline
+        pin = lambda t: t.contiguous().pin_memory()
+        pipe = HostPipeline(1, h, n, d, dtype, dev, rows=rows.stop - rows.start, chunk_rows=24)
+        res = pipe.run(pin(q[:, :, rows]), pin(k[:, :, rows]), pin(v[:, :, rows]), pin(b),
+                       pin(m[:, rows]), do=pin(do[:, :, rows]), group=dist.group.WORLD)
+        torch.cuda.synchronize()
+        same.append(torch.equal(res["o"], ow[:, :, rows].cpu()))
+        same.append(torch.equal(res["dk"], kw.grad[:, :, rows].cpu()))
+        host_db_err = float((res["db"].float() - bw.grad.float().cpu()).abs().max() /
+                            bw.grad.float().abs().max())
+        out.put((rank, same, max(db_err, host_db_err)))
     finally:
         dist.destroy_process_group()
 
