@@ -212,7 +212,7 @@ def test_full_size_against_chunked_oracle(name):
     row chunks (rows are independent; db accumulates over chunks).  bf16 bound:
     max|x - ref| / max|ref| <= 2e-2 for o, dq, dk, dv and <= 3e-2 for db, i.e. a few
     bf16 roundings of the largest value (the same-dtype PyTorch error on smaller
-    problems of this family is 1e-2 .. 9e-2, see DESIGN.md)."""
+    problems of this family is 1e-2 .. 9e-2)."""
     w = WORKLOADS[name]
     q, k, v, b, m, do = make_inputs(w, seed=1337, device=DEV)
     got = run_kernel(q, k, v, b, m, do)
