@@ -224,6 +224,25 @@ def test_full_size_against_chunked_oracle(name):
         assert e <= tol, f"{name} {nm}: rel err {e:.3e} > {tol}"
 
 
+@pytest.mark.parametrize("name", ["c2_n256", "c3_n512_pad", "c4_n1024_h8_d64_fwd", "c5_n2048_pad",
+                                  "metric_n1024"])
+def test_configured_workloads_run_on_tensor_cores(name, monkeypatch):
+    """With the kernel choice forced to tcgen05 an unsupported problem is an error instead
+    of a silent fall-back to the CUDA-core kernels: every 16-bit workload of the table must
+    pass (a few pair rows are enough: the tile plan depends on n, h, d and the dtype)."""
+    monkeypatch.setenv("TRIFAST_B200_KERNEL", "tcgen05")
+    w = WORKLOADS[name]
+    q, k, v, b, m, do = make_inputs(w, seed=3, device=DEV, sample_rows=6)
+    got = run_kernel(q, k, v, b, m, do) if w.backward else None
+    if got is None:
+        o = triangle_attention(q, k, v, b, m)
+        torch.cuda.synchronize()
+        got = (o.float().cpu(),)
+    cpu = [t.float().cpu() for t in (q, k, v, b)]
+    ref, _ = orc.forward(cpu[0], cpu[1], cpu[2], cpu[3], m.cpu(), torch.float32)
+    assert rel_err(got[0], ref) < 2e-2
+
+
 def test_opcheck():
     """torch.library.opcheck on the forward op (tests/unit/test_trifast_opcheck.py:7-13)."""
     from torch.library import opcheck

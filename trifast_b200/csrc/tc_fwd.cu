@@ -77,9 +77,15 @@ struct FwdCfg {
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
   // per softmax warp: 4 mask words per 128-key chunk, two buffers (this item's and the next's)
-  static int mask_bytes(int n) { return 2 * 4 * R * ((n + kBK - 1) / kBK) * 16; }
+  static int mask_bytes(int n, int bufs) { return bufs * 4 * R * ((n + kBK - 1) / kBK) * 16; }
+  static int smem_with(int n, int bufs) {
+    const int head = (kHeaderBytes + mask_bytes(n, bufs) + 1023) / 1024 * 1024;
+    return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
+  }
+  // two mask buffers (the next item's words are made ahead) when they fit, else one
+  static int mask_bufs(int n) { return smem_with(n, 2) <= kSmemLimit ? 2 : 1; }
   static int smem_bytes(int n) {
-    const int head = (kHeaderBytes + mask_bytes(n) + 1023) / 1024 * 1024;
+    const int head = (kHeaderBytes + mask_bytes(n, mask_bufs(n)) + 1023) / 1024 * 1024;
     return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
   }
 };
@@ -90,7 +96,8 @@ struct ItemGrid {
   int njt, nrp, total;
 };
 
-template <typename T, int D, int R, int NS>
+// MB: mask buffers per softmax warp (2: the next item's words are made ahead).
+template <typename T, int D, int R, int NS, int MB>
 __global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
@@ -114,7 +121,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
-  const uint32_t tiles_off = (kHeaderBytes + 2 * 4 * R * nkt * 16 + 1023u) & ~1023u;
+  const uint32_t tiles_off = (kHeaderBytes + MB * 4 * R * nkt * 16 + 1023u) & ~1023u;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kTileBytes; };
@@ -278,7 +285,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + r * 256;
     const uint32_t tP = tS + 128, tO = tS + 192;
-    uint32_t* mb = maskbits + warp * 2 * nkt * 4;  // this warp's own two copies: no cross-warp sync
+    uint32_t* mb = maskbits + warp * MB * nkt * 4;  // this warp's own copies: no cross-warp sync
 
     // Key mask of a row as bit words (bit set = key dropped or beyond n), made one item
     // ahead so that the loads run under the last PV of the current item.  Lane l reads
@@ -332,13 +339,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     int g = 0, it = 0;
     bool ok = true;
+    constexpr bool ahead = MB == 2;
     RowMask next_mask{mb, false};
-    if ((int)blockIdx.x < items.total) next_mask = row_mask(blockIdx.x, mb);
+    if (ahead && (int)blockIdx.x < items.total) next_mask = row_mask(blockIdx.x, mb);
     for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
       const Item im = decode(w);
       const int i = slot_row(im, r);
       const bool do_store = im.i0 + r < dm.n_rows;
       const int b = im.b, h = im.h, jt = im.jt;
+      if (!ahead) next_mask = row_mask(w, mb);  // one buffer: made at the top of the item
       const bool row_full = next_mask.full;
       const uint32_t* mbr = next_mask.words;
 
@@ -487,7 +496,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       if (!ok) break;
 
       // the next item's mask words, while the last PV of this item runs
-      if (w + (int)gridDim.x < items.total)
+      if (ahead && w + (int)gridDim.x < items.total)
         next_mask = row_mask(w + gridDim.x, mb + ((it + 1) & 1) * nkt * 4);
 
       // epilogue of the item: O / l and lse
@@ -581,7 +590,8 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
       return cudaErrorInvalidValue;
   }
   const int smem = Cfg::smem_bytes(dm.n);
-  auto kern = tc_fwd_kernel<T, D, R, NS>;
+  const bool two = Cfg::mask_bufs(dm.n) == 2;
+  auto kern = two ? tc_fwd_kernel<T, D, R, NS, 2> : tc_fwd_kernel<T, D, R, NS, 1>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   ItemGrid items;
