@@ -16,7 +16,7 @@ from oracle import triangle_oracle as orc
 from tests.helpers import (DTYPE_EPS, FP32_REL_TOL, assert_direction, assert_within_pt_error,
                            golden_cases, load_golden, rel_err)
 from trifast_b200 import triangle_attention
-from trifast_b200.configs import WORKLOADS, make_inputs
+from trifast_b200.configs import WORKLOADS, Workload, make_inputs
 from trifast_b200.utils import gen_tensors
 
 pytestmark = pytest.mark.gpu
@@ -224,14 +224,22 @@ def test_full_size_against_chunked_oracle(name):
         assert e <= tol, f"{name} {nm}: rel err {e:.3e} > {tol}"
 
 
+_EXTRA_TC_SHAPES = {
+    # head dim 64 with the backward, at the largest n of the table and with a ragged n
+    "n2048_h2_d64_bwd": Workload("n2048_h2_d64_bwd", 2048, 2, 64, torch.float16, "random:0.2"),
+    "n1001_h2_d64_bwd": Workload("n1001_h2_d64_bwd", 1001, 2, 64, torch.bfloat16, "padding:0.9"),
+    "n4096_h1_d32_bwd": Workload("n4096_h1_d32_bwd", 4096, 1, 32, torch.bfloat16, "none"),
+}
+
+
 @pytest.mark.parametrize("name", ["c2_n256", "c3_n512_pad", "c4_n1024_h8_d64_fwd", "c5_n2048_pad",
-                                  "metric_n1024"])
+                                  "metric_n1024"] + sorted(_EXTRA_TC_SHAPES))
 def test_configured_workloads_run_on_tensor_cores(name, monkeypatch):
     """With the kernel choice forced to tcgen05 an unsupported problem is an error instead
     of a silent fall-back to the CUDA-core kernels: every 16-bit workload of the table must
     pass (a few pair rows are enough: the tile plan depends on n, h, d and the dtype)."""
     monkeypatch.setenv("TRIFAST_B200_KERNEL", "tcgen05")
-    w = WORKLOADS[name]
+    w = WORKLOADS.get(name) or _EXTRA_TC_SHAPES[name]
     q, k, v, b, m, do = make_inputs(w, seed=3, device=DEV, sample_rows=6)
     got = run_kernel(q, k, v, b, m, do) if w.backward else None
     if got is None:

@@ -76,8 +76,8 @@ struct FwdCfg {
   static constexpr int kThreads = R * 128 + 128;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
-  // per softmax warp: 4 mask words per 128-key chunk, two buffers (this item's and the next's)
-  static int mask_bytes(int n, int bufs) { return bufs * 4 * R * ((n + kBK - 1) / kBK) * 16; }
+  // per slot: 4 mask words per 128-key chunk, one or two buffers (this item's and the next's)
+  static int mask_bytes(int n, int bufs) { return bufs * R * ((n + kBK - 1) / kBK) * 16; }
   static int smem_with(int n, int bufs) {
     const int head = (kHeaderBytes + mask_bytes(n, bufs) + 1023) / 1024 * 1024;
     return 1024 + head + kTilesBytes;                     // 1024: manual base alignment
@@ -117,11 +117,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint8_t* gbase = smem_raw + (base - raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + 256);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
-  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [4R warps][2][nkt][4]
+  uint32_t* maskbits = reinterpret_cast<uint32_t*>(gbase + kHeaderBytes);  // [R slots][MB][nkt][4]
 
   const int n = dm.n;
   const int nkt = (n + kBK - 1) / kBK;
-  const uint32_t tiles_off = (kHeaderBytes + MB * 4 * R * nkt * 16 + 1023u) & ~1023u;
+  const uint32_t tiles_off = (kHeaderBytes + MB * R * nkt * 16 + 1023u) & ~1023u;
   const uint32_t tiles = base + tiles_off;
   auto bar = [&](int i) -> uint32_t { return base + 8u * i; };
   auto q_tile = [&](int r) -> uint32_t { return tiles + r * Cfg::kTileBytes; };
@@ -285,7 +285,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + r * 256;
     const uint32_t tP = tS + 128, tO = tS + 192;
-    uint32_t* mb = maskbits + warp * MB * nkt * 4;  // this warp's own copies: no cross-warp sync
+    // One copy per slot: the four warps of a slot work on the same row, each makes the
+    // same words and writes them to the same place, and reads them back after its own
+    // writes: whatever the interleaving, every read sees the one value all warps write.
+    uint32_t* mb = maskbits + r * MB * nkt * 4;
 
     // Key mask of a row as bit words (bit set = key dropped or beyond n), made one item
     // ahead so that the loads run under the last PV of the current item.  Lane l reads
