@@ -66,6 +66,13 @@ typedef enum trifast_kernel {
   TRIFAST_KERNEL_TCGEN05 = 2 /* tcgen05 / TMEM / TMA kernels: bf16 and fp16 */
 } trifast_kernel;
 
+/* Debug overrides of the heuristic (trifast_shape.flags).  They stand in for the
+ * reference's TRIFAST_FORCE_TUNE switch (src/trifast/autotune_helpers.py:12-14):
+ * a way to make a non-default kernel run, for A/B measurements and tests. */
+typedef enum trifast_flags {
+  TRIFAST_FLAG_SPLIT_BWD = 1 /* dq and dk/dv as two kernels even where the one-pass kernel fits */
+} trifast_flags;
+
 /* Problem extents, shared by every call. */
 typedef struct trifast_shape {
   int32_t batch;
@@ -75,7 +82,7 @@ typedef struct trifast_shape {
   int32_t d;       /* head dim: 16, 32, 64 or 128 */
   int32_t dtype;   /* trifast_dtype of q, k, v, bias, o and the gradients */
   int32_t kernel;  /* trifast_kernel; 0 = heuristic */
-  int32_t reserved;
+  int32_t flags;   /* OR of trifast_flags; 0 = the heuristic decides everything */
 } trifast_shape;
 
 /* (b, h, i, j, d) tensor: strides in elements for b, h, i, j; d has stride 1. */
@@ -104,7 +111,8 @@ typedef struct trifast_plan {
   int32_t rows_per_cta;  /* pair rows sharing one bias tile in the forward */
   int32_t stages;        /* K/V/bias pipeline depth */
   int32_t db_row_splits; /* row groups whose db partials are summed in fixed order */
-  int32_t reserved[2];
+  int32_t bwd_fused;     /* 1: dq, dk, dv come from one kernel (one exponential per score) */
+  int32_t reserved;
 } trifast_plan;
 
 /* Library version as major*10000 + minor*100 + patch. */
@@ -191,6 +199,22 @@ int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
  * TRIFAST_OK or TRIFAST_ERR_DEVICE_TIMEOUT.  (No reference counterpart: Triton
  * kernels have no such waits.) */
 int trifast_check_device_status(void* stream);
+
+/* Enqueues, on `stream`, a copy of the same status word into *host_word without
+ * synchronising or clearing anything.  With host_word in pinned host memory a
+ * binding can call this after each launch and look at the word at the start of its
+ * next call: a non-zero value means some earlier kernel gave up on a wait (its
+ * outputs are not valid), and trifast_check_device_status() then reads and clears
+ * it.  This is how the Python operators turn a device-side timeout into an
+ * exception without a synchronisation per call.  (No reference counterpart.) */
+int trifast_snapshot_device_status(uint32_t* host_word, void* stream);
+
+/* Test support for that path: launches one warp that waits, with the same bounded
+ * wait the kernels use, on a barrier nobody arrives on; after limit_us
+ * microseconds (1 .. 100000) the wait gives up, the kernel sets the status word
+ * and exits normally.  Nothing traps, faults or spins beyond the limit.  (No
+ * reference counterpart.) */
+int trifast_debug_wait_probe(uint32_t limit_us, void* stream);
 
 /* The whole backward (same results as trifast_backward) for callers that cannot
  * allocate device memory: a runtime that gave the whole GPU to its own pool at

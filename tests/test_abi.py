@@ -85,7 +85,7 @@ def test_db_splits_cover_small_problems():
     (dict(batch=0), -2), (dict(kernel=9), -10),
 ])
 def test_shape_validation(kw, rc):
-    f = dict(batch=1, heads=2, n=64, n_rows=64, d=32, dtype=1, kernel=0, reserved=0)
+    f = dict(batch=1, heads=2, n=64, n_rows=64, d=32, dtype=1, kernel=0, flags=0)
     f.update(kw)
     shp = _lib.Shape(**f)
     plan = _lib.Plan()

@@ -16,13 +16,14 @@ LIB_PATH = os.path.join(_HERE, "libtrifast_b200.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+FLAG_SPLIT_BWD = 1                # trifast_flags of the header
 STATIC_SCRATCH_BYTES = 16 << 20   # TRIFAST_STATIC_SCRATCH_BYTES of the header
 _KERNEL_ENV = {"": 0, "auto": 0, "simt": 1, "tcgen05": 2}
 
 
 class Shape(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
-                ("batch", "heads", "n", "n_rows", "d", "dtype", "kernel", "reserved")]
+                ("batch", "heads", "n", "n_rows", "d", "dtype", "kernel", "flags")]
 
 
 class T5(C.Structure):
@@ -40,7 +41,7 @@ class Mask(C.Structure):
 class Plan(C.Structure):
     _fields_ = [("kernel", C.c_int32), ("block_j", C.c_int32), ("block_k", C.c_int32),
                 ("rows_per_cta", C.c_int32), ("stages", C.c_int32), ("db_row_splits", C.c_int32),
-                ("reserved", C.c_int32 * 2)]
+                ("bwd_fused", C.c_int32), ("reserved", C.c_int32)]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/trifast_b200.h
@@ -64,6 +65,8 @@ SIGNATURES = {
                                         C.c_void_p, C.c_size_t, C.c_void_p]),
     "trifast_db_finalize": (C.c_int, [_P(Shape), C.c_void_p, _P(T4), C.c_void_p]),
     "trifast_check_device_status": (C.c_int, [C.c_void_p]),
+    "trifast_snapshot_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "trifast_debug_wait_probe": (C.c_int, [C.c_uint32, C.c_void_p]),
     "trifast_backward_static_scratch": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4),
                                                   _P(Mask), _P(T5), C.c_void_p, _P(T5), _P(T5),
                                                   _P(T5), _P(T4), C.c_void_p]),
@@ -97,16 +100,63 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what}: {status_str(rc)} (status {rc})")
 
 
+# Per-device pinned host word that mirrors the device status word (see
+# trifast_snapshot_device_status in the header): the library copies the status
+# into it after every operator call, and the next call looks at it first.
+_status_words: dict = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_words[idx] = w
+    return w
+
+
+def raise_if_device_gave_up(device) -> None:
+    """First thing in every operator call.  If an earlier kernel on this device gave
+    up on one of its bounded waits, its outputs (and those of every launch since) were
+    never written: read and clear the status and raise, instead of returning
+    uninitialised memory.  Costs one host-memory read when nothing is wrong."""
+    w = _status_word(device)
+    if int(w[0]) == 0:
+        return
+    w.zero_()
+    with torch.cuda.device(device):
+        load().trifast_check_device_status(
+            C.c_void_p(torch.cuda.current_stream(device).cuda_stream))
+    raise RuntimeError(
+        "trifast_b200: " + status_str(-11) + " in an earlier call on this device; the results "
+        "of that call and of the calls after it are invalid (status cleared, retry is possible)")
+
+
+def snapshot_status(device, stream: C.c_void_p) -> None:
+    """Last thing in every operator call: enqueue the copy of the status word."""
+    with torch.cuda.device(device):
+        check(load().trifast_snapshot_device_status(C.c_void_p(_status_word(device).data_ptr()),
+                                                    stream), "trifast_snapshot_device_status")
+
+
 def kernel_choice() -> int:
     """Debug override of the tile heuristic: TRIFAST_B200_KERNEL=simt|tcgen05|auto."""
     return _KERNEL_ENV[os.environ.get("TRIFAST_B200_KERNEL", "").lower()]
 
 
-def make_shape(batch, heads, n, n_rows, d, dtype, kernel=None) -> Shape:
+def flags_choice() -> int:
+    """Debug override: TRIFAST_B200_FLAGS=<int>, an OR of the header's trifast_flags."""
+    return int(os.environ.get("TRIFAST_B200_FLAGS", "0") or 0)
+
+
+def make_shape(batch, heads, n, n_rows, d, dtype, kernel=None, flags=None) -> Shape:
     if dtype not in DTYPE_CODE:
         raise TypeError(f"unsupported dtype {dtype}; expected float32, bfloat16 or float16")
     return Shape(batch, heads, n, n_rows, d, DTYPE_CODE[dtype],
-                 kernel_choice() if kernel is None else kernel, 0)
+                 kernel_choice() if kernel is None else kernel,
+                 flags_choice() if flags is None else flags)
 
 
 def t5(t: torch.Tensor) -> T5:

@@ -56,6 +56,7 @@ int check_shape(const trifast_shape* s) {
   if (s->dtype < TRIFAST_F32 || s->dtype > TRIFAST_F16) return TRIFAST_ERR_DTYPE;
   if (s->kernel < TRIFAST_KERNEL_AUTO || s->kernel > TRIFAST_KERNEL_TCGEN05)
     return TRIFAST_ERR_KERNEL_CHOICE;
+  if (s->flags & ~TRIFAST_FLAG_SPLIT_BWD) return TRIFAST_ERR_KERNEL_CHOICE;
   return TRIFAST_OK;
 }
 
@@ -71,6 +72,11 @@ int check_t5(const trifast_t5* t, const trifast_shape* s) {
     if ((t->stride[a] * eb) & 15) return TRIFAST_ERR_STRIDE;
   }
   if (t->stride[3] < s->d) return TRIFAST_ERR_STRIDE;
+  // A stride of 0 (an expanded dimension) cannot be described to TMA; callers
+  // materialise such views first.  Dimensions of extent 1 may carry any stride.
+  const int ext[3] = {s->batch, s->heads, s->n_rows};
+  for (int a = 0; a < 3; ++a)
+    if (ext[a] > 1 && t->stride[a] == 0) return TRIFAST_ERR_STRIDE;
   return TRIFAST_OK;
 }
 
@@ -205,6 +211,10 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   int splits = 1;
   while (splits < 16 && tiles * splits < want && s->n_rows / (splits * 2) >= 8) splits *= 2;
   p->db_row_splits = splits;
+  // dq, dk, dv from one kernel when the dQ of a whole row (D fp32 columns per 128
+  // queries) fits in TMEM beside the other accumulators (192 + 2 D columns)
+  const int64_t dq_cols = (int64_t)((s->n + 127) / 128) * s->d;
+  p->bwd_fused = (tc_db && dq_cols <= 512 - 192 - 2 * s->d && !(s->flags & TRIFAST_FLAG_SPLIT_BWD)) ? 1 : 0;
   return TRIFAST_OK;
 }
 
@@ -402,6 +412,7 @@ int trifast_backward_dqkv(const trifast_shape* shape, const trifast_t5* d_o, con
     if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
     tc = false;
   }
+  if (tc && c.plan.bwd_fused && tc_bwd_fused_supported(a)) return cuda_rc(tc_bwd_dqkv_fused(a, s));
   if ((rc = cuda_rc(tc ? tc_bwd_dq(a, s) : simt_bwd_dq(a, s)))) return rc;
   return cuda_rc(tc ? tc_bwd_dkv(a, s) : simt_bwd_dkv(a, s));
 }
@@ -424,6 +435,11 @@ int trifast_backward(const trifast_shape* shape, const trifast_t5* d_o, const tr
                      void* stream) {
   int rc = check_shape(shape);
   if (rc) return rc;
+  // every argument is checked before the first launch, so that a bad descriptor
+  // never leaves part of the backward enqueued
+  if ((rc = check_t5(dq, shape)) || (rc = check_t5(dk, shape)) || (rc = check_t5(dv, shape)) ||
+      (rc = check_t4(db, shape)))
+    return rc;
   trifast_plan plan;
   if ((rc = pick_plan(shape, &plan))) return rc;
   const Workspace w = carve(shape, plan);
@@ -452,6 +468,26 @@ int trifast_check_device_status(void* stream) {
   cudaMemsetAsync(status, 0, sizeof(host), s);
   cudaStreamSynchronize(s);
   return TRIFAST_ERR_DEVICE_TIMEOUT;
+}
+
+int trifast_snapshot_device_status(uint32_t* host_word, void* stream) {
+  if (!host_word) return TRIFAST_ERR_NULL;
+  int dev;
+  unsigned int* status;
+  int rc = device_setup(&dev, &status);
+  if (rc) return rc;
+  return cuda_rc(cudaMemcpyAsync(host_word, status, sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                 (cudaStream_t)stream));
+}
+
+int trifast_debug_wait_probe(uint32_t limit_us, void* stream) {
+  if (limit_us == 0 || limit_us > 100000u) return TRIFAST_ERR_TOO_LARGE;
+  int dev;
+  unsigned int* status;
+  int rc = device_setup(&dev, &status);
+  if (rc) return rc;
+  // about 2000 clock cycles per microsecond at the B200's 1.97 GHz
+  return cuda_rc(wait_probe((long long)limit_us * 2000LL, status, (cudaStream_t)stream));
 }
 
 }  // extern "C"

@@ -66,6 +66,8 @@ enum DeviceStatusBits : unsigned int {
   kStatusTimeoutBwdDb = 2u,
   kStatusTimeoutBwdDq = 4u,
   kStatusTimeoutBwdDkv = 8u,
+  kStatusTimeoutBwdFused = 16u,
+  kStatusTimeoutProbe = 32u,
 };
 
 }  // namespace trifast

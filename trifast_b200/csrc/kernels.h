@@ -62,5 +62,11 @@ bool tc_backward_supported(const BwdArgs& a);
 cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s);
 cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s);
 cudaError_t tc_bwd_db(const BwdArgs& a, cudaStream_t s);
+// dq, dk and dv in one pass over the scores, when a whole row's dQ fits in TMEM
+bool tc_bwd_fused_supported(const BwdArgs& a);
+cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s);
+
+// One warp whose bounded wait runs out after limit_cycles (test support).
+cudaError_t wait_probe(long long limit_cycles, unsigned int* status, cudaStream_t s);
 
 }  // namespace trifast

@@ -1,7 +1,7 @@
 // Bias gradient db[j, k] = sum over pair rows i of dS[i, j, k] on the tensor cores.
 //
 // A work item is a 128 x 128 (j, k) tile of one (b, h) and one block of pair rows
-// (a "row split"); the launch gives every CTA one item.  Per row of its item the CTA
+// (a "row split"); every CTA works on exactly one item (blockIdx.x).  Per row of its item the CTA
 // recomputes
 //     S  = Q_i K_i^T,   dP = dO_i V_i^T        (two SS MMAs, 128 x 128 each)
 //     P  = exp2(S * c + bias * log2e - lse_i * log2e),   dS = P * (dP - delta_i)
@@ -34,7 +34,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 // the math warpgroups gain must not exceed what the issue warpgroup releases (the
 // registers a CTA did not get at launch are not part of the pool), or the request
 // blocks forever.
-constexpr int kRegsLaunch = 96, kRegsIssue = 56, kRegsMath = 104;
+constexpr int kRegsLaunch = 96, kRegsIssue = 32, kRegsMath = 112;
 static_assert(512 * kRegsMath + 128 * kRegsIssue <= 640 * kRegsLaunch, "setmaxnreg pool");
 constexpr int kTmaWarp = 16, kMmaWarp = 17;
 
@@ -56,7 +56,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_nlse, const __grid_constant__ CUtensorMap map_delta,
              View4 bias, const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits,
-             int mask_words, float* __restrict__ out, int splits, int total_items, Dims dm,
+             int mask_words, float* __restrict__ out, int splits, Dims dm,
              unsigned int* status) {
   using Cfg = DbCfg<D, NS>;
   constexpr int FULL = 0, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + 2,
@@ -143,16 +143,11 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     if (warp == kTmaWarp) {
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
-        int g = 0;
-        bool ok = true;
-        for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-          const Item im = decode(w);
-          for (int it = 0; it < im.nrows; ++it, ++g) {
-            const int s = g % NS, i = im.i_begin + it;
-            if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) {
-              ok = false;
-              break;
-            }
+        const Item im = decode(blockIdx.x);
+        for (int g = 0; g < im.nrows; ++g) {
+          {
+            const int s = g % NS, i = im.i_begin + g;
+            if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) break;
             mbar_arrive_expect_tx(bar(FULL + s), Cfg::kStageBytes);
             tma_load_5d(q_tile(s), &map_q, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
             tma_load_5d(do_tile(s), &map_do, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
@@ -169,10 +164,9 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t idesc = make_idesc(128, 128, kBf16, false, false);
         bool ok = true;
-        int g = 0;
-        for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-          const int nrows = decode(w).nrows;
-          for (int it = 0; it < nrows && ok; ++it, ++g) {
+        {
+          const int nrows = decode(blockIdx.x).nrows;
+          for (int g = 0; g < nrows && ok; ++g) {
             const int s = g % NS, u = g & 1;
             ok = mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag);
             if (ok && g >= 2) ok = mbar_wait(bar(S_FREE + u), ((g >> 1) - 1) & 1, abort_flag);
@@ -205,12 +199,17 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     const float uniform = 1.f / (float)n;
 
     bool ok = true;
-    int g = 0;
-    for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-      const Item im = decode(w);
+    {
+      const Item im = decode(blockIdx.x);
       const int b = im.b, h = im.h, kt = im.kt;
       const int j = im.jt * 128 + row;
       const int key0 = kt * 128 + quarter * 32;
+
+      // where this thread's 32 sums go, settled now so that the item's indices need not
+      // stay live through the row loop
+      float* const dst =
+          out + (((int64_t)im.split * dm.batch * dm.heads + im.bh) * n + min(j, n - 1)) * n + key0;
+      const int n_store = (j < n) ? min(32, n - key0) : 0;  // <= 0: nothing to store
 
       float acc[32];
       uint32_t bp[16];  // this thread's 32 bias values, kept as 16-bit pairs
@@ -239,8 +238,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
         }
       }
-      for (int it = 0; it < im.nrows; ++it, ++g) {
-        const int s = g % NS, u = g & 1, i = im.i_begin + it;
+      for (int g = 0; g < im.nrows; ++g) {
+        const int s = g % NS, u = g & 1, i = im.i_begin + g;
         // per-row inputs that do not come through shared memory (consumed after the
         // barrier waits below, which hide their latency)
         const uint32_t mw =
@@ -300,17 +299,15 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
         }
       }
-      if (!ok) break;
-      if (j < n) {
-        float* dst = out + (((int64_t)im.split * dm.batch * dm.heads + im.bh) * n + j) * n + key0;
-        if (key0 + 32 <= n && (n & 3) == 0) {
+      if (ok && n_store > 0) {
+        if (n_store == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4)
             *reinterpret_cast<float4*>(dst + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c)
-            if (key0 + c < n) dst[c] = acc[c];
+            if (c < n_store) dst[c] = acc[c];
         }
       }
     }
@@ -365,10 +362,7 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   const int t = (dm.n + 127) / 128;
   const int total = t * t * a.splits * dm.batch * dm.heads;
-  // One item per CTA.  (The kernel loops over items c, c + grid, ..., but with
-  // grid < total a rare wrong row sum showed up in items after a CTA's first; until
-  // that is understood every CTA gets exactly one item.)
-  const int grid = total;
+  const int grid = total;  // one item per CTA
   float* out = a.splits > 1 ? a.db_partials : a.db_f32;
   View4 bias = a.bias;
   if (a.bias_pad) {  // the copy with a 16-byte row pitch: its rows can be read 16 bytes at a time
@@ -378,8 +372,7 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
     bias.sb = bias.sh * dm.heads;
   }
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mnl, mdl, bias, a.rowfull,
-                                              a.maskbits_lin, a.mask_words, out, a.splits, total, dm,
-                                              a.status);
+                                              a.maskbits_lin, a.mask_words, out, a.splits, dm, a.status);
   return cudaGetLastError();
 }
 

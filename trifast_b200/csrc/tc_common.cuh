@@ -81,11 +81,61 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
 constexpr uint32_t kParkNs = 20000;              // re-check abort flag and clock every 20 us
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// The wait itself, with the limit as an argument (clock cycles).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity,
+                                                volatile int* abort_flag, long long limit_cycles) {
   if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, kWaitCycles);
+}
+
+// The same bounded wait for the warps that issue MMAs and TMA loads: it polls with
+// the non-blocking test instead of parking the thread, because a parked thread is
+// resumed some hundreds of cycles after the phase completes and every such delay
+// sits on the critical path between a tile being ready and its MMAs being issued.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// Two barriers at once (the second only when `with_b`): both tests are issued before
+// either result is looked at, so their shared-memory round trips overlap.
+__device__ __forceinline__ bool mbar_wait_spin2(uint32_t bar_a, uint32_t parity_a, bool with_b,
+                                                uint32_t bar_b, uint32_t parity_b,
+                                                volatile int* abort_flag) {
+  bool a = mbar_test_wait(bar_a, parity_a);
+  bool b = !with_b || mbar_test_wait(bar_b, parity_b);
+  if (a && b) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (!a) a = mbar_test_wait(bar_a, parity_a);
+      if (!b) b = mbar_test_wait(bar_b, parity_b);
+      if (a && b) return true;
+    }
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;

@@ -21,7 +21,8 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .torch import _check_inputs, _prep4, _prep5, _prep_mask, _stream, _triangle_attention
+from .torch import (_check_inputs, _check_saved, _prep4, _prep5, _prep_mask, _stream,
+                    _triangle_attention)
 
 
 def shard_rows(n: int, rank: int, world: int) -> slice:
@@ -49,6 +50,8 @@ class CudaKernels:
     def backward_db(self, do, q, k, v, b, mask, o, lse):
         """Returns (db_f32 partial over the local rows, workspace holding delta)."""
         lib = _lib.load()
+        _check_saved(do, q, o, lse)
+        _lib.raise_if_device_gave_up(q.device)
         shp, (do, q, k, v), b, m8, (bs, h, n_rows, n, d) = self._common(do, q, k, v, b, mask)
         o, lse = _prep5(o), lse.contiguous()
         nbytes = lib.trifast_backward_workspace_bytes(C.byref(shp))
@@ -77,6 +80,7 @@ class CudaKernels:
                 C.byref(_lib.t5(dv)), C.c_void_p(ws.data_ptr()), C.c_size_t(ws.numel()),
                 _stream(q))
         _lib.check(rc, "trifast_backward_dqkv")
+        _lib.snapshot_status(q.device, _stream(q))
         return dq, dk, dv
 
     def db_finalize(self, db_f32, dtype):

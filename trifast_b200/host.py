@@ -134,6 +134,7 @@ class HostPipeline:
         src = dict(q=q, k=k, v=v, do=do)
 
         lib, L = self.lib, _lib
+        L.raise_if_device_gave_up(self.device)
         cur = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_stream(cur)
@@ -220,6 +221,7 @@ class HostPipeline:
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_run)
         cur.wait_stream(self.s_in)
+        L.snapshot_status(self.device, C.c_void_p(cur.cuda_stream))
         self.kernel_launches = launches
         return out
 

@@ -24,7 +24,9 @@ def _row_vector_ok(t: torch.Tensor) -> bool:
     if t.stride(-1) != 1 or t.data_ptr() % 16:
         return False
     es = t.element_size()
-    return all(s >= 0 and (s * es) % 16 == 0 for s in t.stride()[:-1]) and t.stride(-2) >= t.shape[-1]
+    # a stride of 0 (an expanded dimension) cannot be described to TMA
+    return all((s > 0 or n == 1) and (s * es) % 16 == 0 for s, n in zip(t.stride()[:-1], t.shape[:-1])) \
+        and t.stride(-2) >= t.shape[-1]
 
 
 def _prep5(t):
@@ -56,9 +58,27 @@ def _check_inputs(q, k, v, b, mask):
         raise ValueError(f"mask must be {(bs, n_rows, n)}; got {tuple(mask.shape)}")
     if not (q.dtype == k.dtype == v.dtype == b.dtype):
         raise TypeError("q, k, v and bias must share one dtype")
+    for name, t in (("k", k), ("v", v), ("bias", b), ("mask", mask)):
+        if t.device != q.device:
+            raise ValueError(f"{name} is on {t.device} but q is on {q.device}: every tensor "
+                             "must live on the same CUDA device")
     if not q.is_cuda:
         raise RuntimeError("trifast_b200 runs on CUDA devices only (there is no CPU path)")
     return bs, h, n_rows, n, d
+
+
+def _check_saved(do, q, o, l):
+    """The backward's extra arguments: dO and o like q, lse fp32 (b, h, rows, n)."""
+    bs, h, n_rows, n, d = q.shape
+    for name, t in (("do", do), ("o", o)):
+        if tuple(t.shape) != tuple(q.shape) or t.dtype != q.dtype:
+            raise ValueError(f"{name} must be {tuple(q.shape)} {q.dtype}; got {tuple(t.shape)} {t.dtype}")
+        if t.device != q.device:
+            raise ValueError(f"{name} is on {t.device} but q is on {q.device}")
+    if tuple(l.shape) != (bs, h, n_rows, n) or l.dtype != torch.float32:
+        raise ValueError(f"lse must be float32 {(bs, h, n_rows, n)}; got {l.dtype} {tuple(l.shape)}")
+    if l.device != q.device:
+        raise ValueError(f"lse is on {l.device} but q is on {q.device}")
 
 
 def _stream(t):
@@ -70,6 +90,7 @@ def _triangle_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: to
                         mask: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     bs, h, n_rows, n, d = _check_inputs(q, k, v, b, mask)
     lib = _lib.load()
+    _lib.raise_if_device_gave_up(q.device)
     q, k, v, b = _prep5(q), _prep5(k), _prep5(v), _prep4(b)
     m8 = _prep_mask(mask)
     o = torch.empty((bs, h, n_rows, n, d), dtype=q.dtype, device=q.device)
@@ -85,6 +106,7 @@ def _triangle_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: to
                                  C.c_void_p(ws.data_ptr() if ws is not None else None),
                                  C.c_size_t(ws_bytes), _stream(q))
     _lib.check(rc, "trifast_forward")
+    _lib.snapshot_status(q.device, _stream(q))
     return o, lse
 
 
@@ -102,7 +124,9 @@ def triangle_attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
                            ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
                                       torch.Tensor]:
     bs, h, n_rows, n, d = _check_inputs(q, k, v, b, mask)
+    _check_saved(do, q, o, l)
     lib = _lib.load()
+    _lib.raise_if_device_gave_up(q.device)
     do, q, k, v, o, b = _prep5(do), _prep5(q), _prep5(k), _prep5(v), _prep5(o), _prep4(b)
     m8 = _prep_mask(mask)
     l = l.contiguous()
@@ -121,6 +145,7 @@ def triangle_attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
             C.byref(_lib.t5(dk)), C.byref(_lib.t5(dv)), C.byref(_lib.t4(db)),
             C.c_void_p(ws.data_ptr()), C.c_size_t(ws_bytes), _stream(q))
     _lib.check(rc, "trifast_backward")
+    _lib.snapshot_status(q.device, _stream(q))
     return dq, dk, dv, db, dmask
 
 
