@@ -12,8 +12,15 @@ Keys beyond the usual ones:
   value / ms_per_step : kernels only, inputs resident in HBM, CUDA events, max over ranks
   e2e                 : the same step through the package's host-resident API with pinned-host
                         inputs copied in and o, dq, dk, dv, db copied out every step
-  roofline            : the dominant kernel phase against the measured bf16 tensor peak
-  phases_ms           : forward / db / dq+dk+dv phase times (CUDA events, N = 1)
+  public_api          : the same step through trifast_b200.triangle_attention(...) and
+                        o.backward(dO) (the row-sharded operator at N > 1): allocator, operator
+                        dispatch and autograd included
+  roofline            : the dominant single kernel against the measured bf16 tensor peak,
+                        with the FLOP count used
+  phases_ms           : forward / db / dq+dk+dv phase times of this rank (CUDA events); at
+                        N > 1 also the exposed part of the db all-reduce
+  parity_ok           : N > 1 only: rank 0 repeats the whole problem alone and compares o
+                        (bit for bit on its rows, checksum over all ranks) and the reduced db
   cpu_baseline        : the PyTorch CPU restatement on a bounded row sample (N = 1)
 
 ``--impl reference`` times the reference algorithm's CPU implementation (the
@@ -176,6 +183,8 @@ def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # every host core, also under torchrun (which exports OMP_NUM_THREADS=1)
+    torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     rows = cpu_rows_for_budget(w, 4.0)
     step = cpu_sample_step(w, rows)
@@ -248,7 +257,8 @@ class DirectStep:
         self.launches = 1
         if w.backward:
             self.launches += 1 + (1 if plan["kernel"] == 2 else 0) + 1 + 1 + \
-                (1 if plan["db_row_splits"] > 1 else 0) + 2 + 1
+                (1 if plan["db_row_splits"] > 1 else 0) + (1 if plan["bwd_fused"] else 2) + 1
+        self.exposed = None   # (event after dq/dk/dv, event after the all-reduce wait)
 
     def forward(self):
         a, B = self.a, C.byref
@@ -290,7 +300,11 @@ class DirectStep:
             work = dist.all_reduce(self.db32, async_op=True)
         self.backward_dqkv()
         if work is not None:
+            if self.exposed is not None:
+                self.exposed[0].record()
             work.wait()
+            if self.exposed is not None:
+                self.exposed[1].record()
         self.finalize()
 
 
@@ -361,6 +375,54 @@ def run_native(args, w):
     rc = step.lib.trifast_check_device_status(step.stream)
     step._lib.check(rc, "device status after the timed region")
 
+    # ---- the same step through the public operator (allocations, dispatch, autograd) ----
+    from trifast_b200 import triangle_attention
+    qa, ka, va, ba = (t.detach().requires_grad_(w.backward) for t in (q, k, v, b))
+
+    def api_step():
+        if world > 1:
+            o_ = triangle_attention_row_sharded(qa, ka, va, ba, m)
+        else:
+            o_ = triangle_attention(qa, ka, va, ba, m)
+        if w.backward:
+            o_.backward(do)
+            qa.grad = ka.grad = va.grad = ba.grad = None
+
+    for _ in range(3):
+        api_step()
+    barrier()
+    api_ms = time_events(api_step, args.steps)
+    barrier()
+    if world > 1:
+        t = torch.tensor([api_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        api_ms = float(t)
+
+    # ---- N > 1: are the sharded results those of one GPU? -------------------------------
+    parity = None
+    if world > 1:
+        step.step()
+        cs = torch.stack([step.o.double().sum(), step.o.double().abs().sum()])
+        dist.all_reduce(cs)
+        if rank == 0:
+            fq, fk, fv, fb, fm, fdo = make_inputs(w, seed=0, device=dev)
+            full = DirectStep(w, fq, fk, fv, fb, fm, fdo, 1)
+            full.step()
+            torch.cuda.synchronize()
+            ref = torch.stack([full.o.double().sum(), full.o.double().abs().sum()])
+            o_rows_equal = bool(torch.equal(full.o[:, :, rows], step.o))
+            sums_equal = bool(torch.allclose(cs, ref, rtol=1e-9, atol=0))
+            parity = {"o_rows_bitwise": o_rows_equal, "o_checksum": sums_equal}
+            if w.backward:
+                num = (step.db.float() - full.db.float()).abs().max()
+                den = full.db.float().abs().max()
+                parity["db_rel_err"] = float(num / den)
+                parity["dq_rows_bitwise"] = bool(torch.equal(full.dq[:, :, rows], step.dq))
+            parity["ok"] = o_rows_equal and sums_equal and parity.get("db_rel_err", 0.0) < 1e-2 \
+                and parity.get("dq_rows_bitwise", True)
+            del full, fq, fk, fv, fb, fm, fdo
+        barrier()
+
     # ---- end to end through the public API with host buffers ---------------------------
     # Pinned host tensors in, pinned host tensors out, through the host-resident entry
     # point of the package (trifast_b200.host): every step copies this rank's q, k, v,
@@ -401,26 +463,50 @@ def run_native(args, w):
     del host, outs_host, pipe
     total_flops = flops_step(w)
 
-    # ---- per-phase timing, roofline and the CPU baseline (single GPU only) ------------
+    # ---- per-phase timing (every N), roofline and the CPU baseline (single GPU only) ---
     phases, roofline, cpu = None, None, None
     peaks = measured_peaks()
     step_q = None
+    phases = {"forward": time_events(step.forward, args.steps)}
+    if w.backward:
+        phases["backward_db"] = time_events(step.backward_db, args.steps)
+        phases["backward_dqkv"] = time_events(step.backward_dqkv, args.steps)
+        phases["db_finalize"] = time_events(step.finalize, args.steps)
+    if world > 1 and w.backward:
+        # the part of the db all-reduce that the dq/dk/dv kernels do not hide: device time
+        # between the end of those kernels and the end of the wait, and the collective alone
+        step.exposed = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        exp = []
+        for _ in range(args.steps):
+            step.step()
+            torch.cuda.synchronize()
+            exp.append(step.exposed[0].elapsed_time(step.exposed[1]))
+        step.exposed = None
+        phases["allreduce_exposed"] = sum(exp) / len(exp)
+        phases["allreduce_alone"] = time_events(lambda: dist.all_reduce(step.db32), args.steps)
+        t = torch.tensor([phases[k_] for k_ in sorted(phases)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        phases = {k_: float(x) for k_, x in zip(sorted(phases), t)}
     if world == 1:
         step_q = quantiles(time_events_each(step.step, max(args.steps, 10)))
-        phases = {"forward": time_events(step.forward, args.steps)}
+        # Algorithmic FLOPs per kernel (4 h n^3 d per contraction pair of the forward):
+        # forward S and PV = 4; the one-pass dq/dk/dv kernel S, dP, dV, dK, dQ = 10 (with two
+        # kernels the phase holds both and S, dP are executed twice: still 10 algorithmic);
+        # db recomputes S and dP = 4 executed, none of them algorithmic beyond the 10.
         kernels_flops = {"forward": flops_fwd(w)}
+        names = {"forward": "tc_fwd_kernel"}
         if w.backward:
-            phases["backward_db"] = time_events(step.backward_db, args.steps)
-            phases["backward_dqkv"] = time_events(step.backward_dqkv, args.steps)
-            # contractions each phase executes: db recomputes S and dP (2 of them);
-            # dq+dk+dv executes S, dP (twice when dq and dk/dv are separate kernels), dQ, dK, dV
-            kernels_flops["backward_db"] = flops_fwd(w)
             kernels_flops["backward_dqkv"] = 2.5 * flops_fwd(w)
-        top = max(phases, key=phases.get)
+            names["backward_dqkv"] = "tc_dqkv_kernel" if step.plan["bwd_fused"] else \
+                "tc_dq_kernel + tc_dkv_kernel"
+        top = max(kernels_flops, key=lambda k_: phases[k_])
         ach = kernels_flops[top] / (phases[top] * 1e-3) / 1e12
         peak = peaks["burst"]
-        roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak,
-                    "unit": "TFLOP/s", "frac": ach / peak,
+        roofline = {"bound": "tensor", "kernel": names[top], "phase": top, "achieved": ach,
+                    "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                    "flops_per_launch": kernels_flops[top],
+                    "flops_formula": "10*b*h*n^3*d" if top == "backward_dqkv" else "4*b*h*n^3*d",
+                    "ms_per_launch": phases[top],
                     "peak_source": f"bf16 burst, {peaks['source']}", "traffic": None,
                     "step_frac_of_peak": total_flops / (ms * 1e-3) / 1e12 / peak,
                     "step_frac_of_sustained": total_flops / (ms * 1e-3) / 1e12 / peaks["sustained"]}
@@ -432,6 +518,7 @@ def run_native(args, w):
         except (OSError, ValueError):
             pass
         if rank == 0 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
             crow = cpu_rows_for_budget(w, 8.0)
             cstep = cpu_sample_step(w, crow)
             cstep()
@@ -453,6 +540,10 @@ def run_native(args, w):
             "plan": step.plan, "clocks": clocks,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "public_api": {"value": total_flops / (api_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "ms_per_step": api_ms,
+                           "call": "triangle_attention_row_sharded" if world > 1 else
+                                   "triangle_attention", "backward": "o.backward(dO)"},
             "gpu_launches": step.launches * args.steps,
             # fraction of the N GPUs' combined dense bf16 tensor peak
             "frac_of_bf16_peak": {
@@ -460,8 +551,11 @@ def run_native(args, w):
                 "measured_sustained": total_flops / (ms * 1e-3) / 1e12 / (peaks["sustained"] * world),
                 "nominal_2250": total_flops / (ms * 1e-3) / 1e12 / (2250.0 * world)},
         }
-        if phases is not None:
-            line["phases_ms"] = phases
+        line["phases_ms"] = phases
+        if parity is not None:
+            line["parity_ok"] = parity["ok"]
+            line["parity"] = parity
+        if roofline is not None:
             line["ms_per_step_quantiles"] = step_q
             line["forward_only"] = {"ms": phases["forward"],
                                     "tflops": flops_fwd(w) / (phases["forward"] * 1e-3) / 1e12}

@@ -58,3 +58,43 @@ def assert_direction(kernel, pt, ref, what):
     sk = float(torch.dot(kernel.double().flatten(), ref.double().flatten())) / rr
     sp = float(torch.dot(pt.double().flatten(), ref.double().flatten())) / rr
     assert sk - sp >= -0.01, f"{what}: projection {sk:.4f} vs pt {sp:.4f}"
+
+
+# ---------------------------------------------------------------------------
+# Direct calls through the C ABI with caller-owned outputs (GPU tests that need to
+# look at the memory around the outputs, or to force a kernel choice per call).
+# ---------------------------------------------------------------------------
+def abi_forward(q, k, v, bias, mask, o, lse, kernel=None, flags=0):
+    import ctypes as C
+    from trifast_b200 import _lib
+    lib = _lib.load()
+    bs, h, rows, n, d = q.shape
+    shp = _lib.make_shape(bs, h, n, rows, d, q.dtype, kernel, flags)
+    wsb = lib.trifast_forward_workspace_bytes(C.byref(shp))
+    ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=q.device)
+    m8 = mask.view(torch.uint8)
+    rc = lib.trifast_forward(C.byref(shp), C.byref(_lib.t5(q)), C.byref(_lib.t5(k)),
+                             C.byref(_lib.t5(v)), C.byref(_lib.t4(bias)), C.byref(_lib.mask_view(m8)),
+                             C.byref(_lib.t5(o)), C.c_void_p(lse.data_ptr()),
+                             C.c_void_p(ws.data_ptr()), C.c_size_t(wsb),
+                             C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc, "trifast_forward")
+
+
+def abi_backward(do, q, k, v, bias, mask, o, lse, dq, dk, dv, db, kernel=None, flags=0):
+    import ctypes as C
+    from trifast_b200 import _lib
+    lib = _lib.load()
+    bs, h, rows, n, d = q.shape
+    shp = _lib.make_shape(bs, h, n, rows, d, q.dtype, kernel, flags)
+    wsb = lib.trifast_backward_workspace_bytes(C.byref(shp))
+    ws = torch.empty(wsb, dtype=torch.uint8, device=q.device)
+    m8 = mask.view(torch.uint8)
+    rc = lib.trifast_backward(
+        C.byref(shp), C.byref(_lib.t5(do)), C.byref(_lib.t5(q)), C.byref(_lib.t5(k)),
+        C.byref(_lib.t5(v)), C.byref(_lib.t4(bias)), C.byref(_lib.mask_view(m8)),
+        C.byref(_lib.t5(o)), C.c_void_p(lse.data_ptr()), C.byref(_lib.t5(dq)),
+        C.byref(_lib.t5(dk)), C.byref(_lib.t5(dv)), C.byref(_lib.t4(db)),
+        C.c_void_p(ws.data_ptr()), C.c_size_t(wsb),
+        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc, "trifast_backward")

@@ -144,3 +144,126 @@ def test_cpu_tensors_are_rejected():
     q, k, v, b, m = gen_tensors(16, 16, 1, False, "cpu", torch.float32)
     with pytest.raises(Exception):
         triangle_attention(q, k, v, b, m)
+
+
+# ---------------------------------------------------------------- debug flags, plan.bwd_fused
+@pytest.mark.parametrize("n,d,dtype,flags,fused", [
+    (1024, 32, torch.bfloat16, 0, 1),    # 8 query tiles x 32 columns of dQ = 256: fits
+    (1025, 32, torch.bfloat16, 0, 0),    # a ninth tile does not
+    (2048, 32, torch.bfloat16, 0, 0),
+    (384, 64, torch.float16, 0, 1),      # 3 x 64 columns next to dK, dV of 64 each
+    (512, 64, torch.float16, 0, 0),
+    (1024, 32, torch.bfloat16, _lib.FLAG_SPLIT_BWD, 0),   # forced two-kernel backward
+    (256, 32, torch.float32, 0, 0),      # CUDA-core path has no fused kernel
+])
+def test_fused_backward_choice(n, d, dtype, flags, fused):
+    plan = _lib.Plan()
+    shp = _lib.make_shape(1, 4, n, n, d, dtype, flags=flags)
+    assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == 0
+    assert plan.bwd_fused == fused
+
+
+def test_unknown_flag_bits_are_rejected():
+    shp = _lib.make_shape(1, 4, 256, 256, 32, torch.bfloat16, flags=2)
+    assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(_lib.Plan())) == -10
+
+
+# ---------------------------------------------------------------- argument checks without a device
+def test_broadcast_strides_are_rejected_before_any_launch():
+    """A stride of 0 on a dimension with more than one entry (an expanded view) cannot be
+    described to TMA: the library names it a stride error instead of failing at launch."""
+    lib = _lib.load()
+    shp = _lib.make_shape(1, 2, 64, 64, 32, torch.bfloat16, 0)
+    t, bias = _fake5(), _lib.T4(0x1000, (C.c_int64 * 3)(2 * 64 * 64, 64 * 64, 64))
+    mask = _lib.Mask(0x1000, (C.c_int64 * 2)(64 * 64, 64))
+    expanded_heads = _fake5(stride=(64 * 64 * 32, 0, 64 * 32, 32))
+    rc = lib.trifast_forward(C.byref(shp), C.byref(expanded_heads), C.byref(t), C.byref(t),
+                             C.byref(bias), C.byref(mask), C.byref(t), C.c_void_p(0x1000), None, 0,
+                             None)
+    assert rc == -5
+    # extent-1 dimensions may carry any stride, 0 included (batch = 1 here)
+    ok_batch = _fake5(stride=(0, 64 * 64 * 32, 64 * 32, 32))
+    rc = lib.trifast_forward(C.byref(shp), C.byref(ok_batch), C.byref(t), C.byref(t), C.byref(bias),
+                             C.byref(mask), C.byref(_fake5(ptr=0)), C.c_void_p(0x1000), None, 0, None)
+    assert rc == -1                                  # got past q; o is the NULL one
+
+
+def test_backward_checks_outputs_before_anything_is_enqueued():
+    lib = _lib.load()
+    shp = _lib.make_shape(1, 2, 64, 64, 32, torch.bfloat16, 0)
+    t, bias = _fake5(), _lib.T4(0x1000, (C.c_int64 * 3)(2 * 64 * 64, 64 * 64, 64))
+    mask = _lib.Mask(0x1000, (C.c_int64 * 2)(64 * 64, 64))
+
+    def call(dq=t, dk=t, dv=t, db=bias):
+        return lib.trifast_backward(C.byref(shp), C.byref(t), C.byref(t), C.byref(t), C.byref(t),
+                                    C.byref(bias), C.byref(mask), C.byref(t), C.c_void_p(0x1000),
+                                    C.byref(dq), C.byref(dk), C.byref(dv), C.byref(db),
+                                    C.c_void_p(0x1000), C.c_size_t(1 << 30), None)
+
+    assert call(dq=_fake5(ptr=0)) == -1
+    assert call(dk=_fake5(ptr=0x1004)) == -6
+    assert call(dv=_fake5(stride=(1, 1, 1, 31))) == -5
+    assert call(db=_lib.T4(0, (C.c_int64 * 3)(2 * 64 * 64, 64 * 64, 64))) == -1
+
+
+def test_probe_and_snapshot_validate_arguments():
+    lib = _lib.load()
+    assert lib.trifast_debug_wait_probe(0, None) == -12
+    assert lib.trifast_debug_wait_probe(100001, None) == -12
+    assert lib.trifast_snapshot_device_status(None, None) == -1
+
+
+def _meta(shape, dtype=torch.bfloat16, device="meta"):
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
+def test_python_layer_rejects_mixed_devices_and_bad_saved_tensors():
+    """Host pointers (or another GPU's) must never reach a kernel: every tensor has to
+    live on q's device, and the backward's dO, o and lse must match q."""
+    from trifast_b200.torch import _check_inputs, _check_saved
+    s5, s4, s3 = (1, 2, 16, 16, 32), (1, 2, 16, 16), (1, 16, 16)
+    q, k, v, b = _meta(s5), _meta(s5), _meta(s5), _meta(s4)
+    m = _meta(s3, torch.bool)
+    for bad in ("k", "v", "bias", "mask"):
+        args = dict(k=k, v=v, bias=b, mask=m)
+        args[bad] = torch.empty(args[bad].shape, dtype=args[bad].dtype, device="cpu")
+        with pytest.raises(ValueError, match="same CUDA device"):
+            _check_inputs(q, args["k"], args["v"], args["bias"], args["mask"])
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        _check_inputs(q, k, v, b, m)                 # consistent, but not CUDA
+    lse = _meta((1, 2, 16, 16), torch.float32)
+    _check_saved(_meta(s5), q, _meta(s5), lse)
+    with pytest.raises(ValueError, match="do must be"):
+        _check_saved(_meta((1, 2, 16, 16, 16)), q, _meta(s5), lse)
+    with pytest.raises(ValueError, match="o must be"):
+        _check_saved(_meta(s5), q, _meta(s5, torch.float16), lse)
+    with pytest.raises(ValueError, match="lse must be float32"):
+        _check_saved(_meta(s5), q, _meta(s5), _meta((1, 2, 16, 16), torch.bfloat16))
+    with pytest.raises(ValueError, match="lse is on"):
+        _check_saved(_meta(s5), q, _meta(s5), torch.empty((1, 2, 16, 16), dtype=torch.float32))
+
+
+def test_expanded_views_are_materialised_by_the_python_layer():
+    from trifast_b200.torch import _row_vector_ok
+    base = torch.zeros(1, 1, 16, 16, 32, dtype=torch.bfloat16)
+    assert _row_vector_ok(base)
+    assert not _row_vector_ok(base.expand(1, 4, 16, 16, 32))     # stride 0 over 4 heads
+    assert _row_vector_ok(base.expand(1, 1, 16, 16, 32))
+
+
+# ---------------------------------------------------------------- static-scratch capacity
+@pytest.mark.parametrize("h,d,dtype,n_ok,n_too_large", [
+    (4, 32, torch.bfloat16, 224, 256),    # tensor-core plan: the row-split db partials dominate
+    (4, 64, torch.float16, 224, 256),
+    (1, 32, torch.bfloat16, 448, 480),
+    (4, 128, torch.bfloat16, 576, 608),   # CUDA-core plan
+    (4, 32, torch.float32, 576, 608),
+])
+def test_static_scratch_capacity(h, d, dtype, n_ok, n_too_large):
+    """trifast_backward_static_scratch serves problems whose backward workspace fits its
+    16 MiB array; these are the largest sizes on either side of that line."""
+    lib = _lib.load()
+    ok = _lib.make_shape(1, h, n_ok, n_ok, d, dtype)
+    big = _lib.make_shape(1, h, n_too_large, n_too_large, d, dtype)
+    assert 0 < lib.trifast_backward_workspace_bytes(C.byref(ok)) <= _lib.STATIC_SCRATCH_BYTES
+    assert lib.trifast_backward_workspace_bytes(C.byref(big)) > _lib.STATIC_SCRATCH_BYTES

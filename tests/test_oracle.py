@@ -94,3 +94,24 @@ def test_work_accounting():
         pytest.approx(1.924e12, rel=1e-3)
     assert orc.hbm_bytes_forward(1, 4, 1024, 32, 2) == pytest.approx(1100e6, rel=2e-2)
     assert orc.hbm_bytes_backward(1, 4, 1024, 32, 2) == pytest.approx(2182e6, rel=2e-2)
+
+
+@pytest.mark.parametrize("case,n,h,d,batch,std,use_mask,seed", [
+    ("ragged17_randmask_fp32", 17, 2, 16, 2, 1.0, True, 1337),
+    ("n19_d128_randmask_fp32", 19, 1, 128, 1, 1.0, True, 5),
+    ("n25_d64_std2_nomask_fp32", 25, 1, 64, 1, 2.0, False, 11),
+])
+def test_gen_tensors_reproduces_the_reference_generator(case, n, h, d, batch, std, use_mask, seed):
+    """The fixtures hold what the reference's own gen_tensors drew after
+    torch.manual_seed(seed) (tests/golden/make_golden.py); this package's generator
+    must draw the same bits: same order (q, k, v, bias, mask), same distributions."""
+    from tests.helpers import load_golden
+    from trifast_b200.utils import gen_tensors
+    t, _ = load_golden(case)
+    torch.manual_seed(seed)
+    q, k, v, b, m = gen_tensors(n, d, h, use_mask, "cpu", dtype=torch.float32, batch=batch, std=std)
+    do = torch.randn(q.shape)                        # the fixture's next draw
+    for name, got in (("q", q), ("k", k), ("v", v), ("bias", b), ("do", do)):
+        assert torch.equal(got.detach(), t[name]), name
+    assert torch.equal(m, t["mask"])
+    assert all(x.requires_grad and x.is_leaf for x in (q, k, v, b))

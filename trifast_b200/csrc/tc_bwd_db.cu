@@ -249,6 +249,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         if (!ok) break;
         const float nl = reinterpret_cast<const float*>(gbase + nlse_off(s))[row];
         const float dl = reinterpret_cast<const float*>(gbase + delta_off(s))[row];
+        const float ndl = -dl;
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(EMPTY + s));
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + u), (g >> 1) & 1, abort_flag));
@@ -276,25 +277,29 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             }
           } else if (mh == 0u) {  // no dropped key: a straight block the compiler can overlap
 #pragma unroll
-            for (int c = 0; c < 16; c += 2) {
-              float b0, b1;
+            for (int c = 0; c < 16; c += 2) {  // packed fp32 pairs: two scores per FMA instruction
+              float b0, b1, t0, t1, a0, a1, s0, s1;
               unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
-              const float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
-              const float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
-              acc[hc * 16 + c] = fmaf(p0, gd[c] - dl, acc[hc * 16 + c]);
-              acc[hc * 16 + c + 1] = fmaf(p1, gd[c + 1] - dl, acc[hc * 16 + c + 1]);
+              ffma2(t0, t1, b0, b1, kLog2e, kLog2e, nl, nl);
+              ffma2(a0, a1, x[c], x[c + 1], c1, c1, t0, t1);
+              const float p0 = ex2(a0), p1 = ex2(a1);
+              fadd2(s0, s1, gd[c], gd[c + 1], ndl, ndl);
+              ffma2(acc[hc * 16 + c], acc[hc * 16 + c + 1], p0, p1, s0, s1, acc[hc * 16 + c],
+                    acc[hc * 16 + c + 1]);
             }
           } else {
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
-              float b0, b1;
+              float b0, b1, t0, t1, a0, a1, s0, s1;
               unpack2<T>(bp[(hc * 16 + c) >> 1], b0, b1);
-              float p0 = ex2(fmaf(x[c], c1, fmaf(b0, kLog2e, nl)));
-              float p1 = ex2(fmaf(x[c + 1], c1, fmaf(b1, kLog2e, nl)));
+              ffma2(t0, t1, b0, b1, kLog2e, kLog2e, nl, nl);
+              ffma2(a0, a1, x[c], x[c + 1], c1, c1, t0, t1);
+              float p0 = ex2(a0), p1 = ex2(a1);
               p0 = ((mh >> c) & 1u) ? 0.f : p0;
               p1 = ((mh >> (c + 1)) & 1u) ? 0.f : p1;
-              acc[hc * 16 + c] = fmaf(p0, gd[c] - dl, acc[hc * 16 + c]);
-              acc[hc * 16 + c + 1] = fmaf(p1, gd[c + 1] - dl, acc[hc * 16 + c + 1]);
+              fadd2(s0, s1, gd[c], gd[c + 1], ndl, ndl);
+              ffma2(acc[hc * 16 + c], acc[hc * 16 + c + 1], p0, p1, s0, s1, acc[hc * 16 + c],
+                    acc[hc * 16 + c + 1]);
             }
           }
         }

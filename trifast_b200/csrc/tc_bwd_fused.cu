@@ -462,17 +462,24 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     unpack2<T>(u.y, bv[2], bv[3]);
                     unpack2<T>(u.z, bv[4], bv[5]);
                     unpack2<T>(u.w, bv[6], bv[7]);
+                    // packed fp32 pairs: two scores per FMA instruction
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                      const float arg = fmaf(x[q8 * 8 + e], c1, fmaf(bv[e], kLog2e, nl[e]));
-                      p[e] = (X & 16) ? arg : ex2(arg);
+                    for (int e = 0; e < 8; e += 2) {
+                      float t0, t1, a0, a1;
+                      ffma2(t0, t1, bv[e], bv[e + 1], kLog2e, kLog2e, nl[e], nl[e + 1]);
+                      ffma2(a0, a1, x[q8 * 8 + e], x[q8 * 8 + e + 1], c1, c1, t0, t1);
+                      p[e] = (X & 16) ? a0 : ex2(a0);
+                      p[e + 1] = (X & 16) ? a1 : ex2(a1);
                     }
                   }
 #pragma unroll
                   for (int e = 0; e < 8; e += 2) {
                     const int c = q8 * 8 + e;
+                    float s0, s1, d0, d1;
+                    ffma2(s0, s1, dl[e], dl[e + 1], -1.f, -1.f, g_[c], g_[c + 1]);   // dP - delta
+                    fmul2(d0, d1, p[e], p[e + 1], s0, s1);
                     uint32_t wp = pack2<T>(p[e], p[e + 1]);
-                    uint32_t wd = pack2<T>(p[e] * (g_[c] - dl[e]), p[e + 1] * (g_[c + 1] - dl[e + 1]));
+                    uint32_t wd = pack2<T>(d0, d1);
                     if (kMode == 1 || kMode == 3) {  // dropped keys weigh exactly zero
                       wp = dropped ? 0u : wp;
                       wd = dropped ? 0u : wd;
