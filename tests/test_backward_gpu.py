@@ -266,3 +266,42 @@ def test_check_device_status_reports_the_probe():
     assert lib.trifast_check_device_status(st) == -11     # synchronises, reports, clears
     assert lib.trifast_check_device_status(st) == 0
     _lib._status_word(torch.device(DEV)).zero_()
+
+
+@pytest.mark.parametrize("n,h,d,dtype", [(40, 2, 32, torch.float32), (136, 2, 32, torch.bfloat16)])
+def test_ending_node_variant(n, h, d, dtype):
+    """The pair-transposed operator against a direct statement of the ending-node formula,
+    forward and (through autograd on that statement) backward."""
+    from trifast_b200 import triangle_attention_ending_node
+    torch.manual_seed(4)
+    q, k, v = ((torch.randn(1, h, n, n, d) * d ** -0.5).to(dtype) for _ in range(3))
+    b = torch.randn(1, h, n, n).to(dtype)
+    m = torch.rand(1, n, n) < 0.25
+    m[:, torch.arange(n), torch.arange(n)] = False
+    do = torch.randn(1, h, n, n, d).to(dtype)
+    ref_in = [t.double().requires_grad_(True) for t in (q, k, v, b)]
+    ref_o = orc.forward_ending_node(*ref_in, m, torch.float64)
+    ref_o.backward(do.double())
+    got_in = [t.to(DEV).requires_grad_(True) for t in (q, k, v, b)]
+    o = triangle_attention_ending_node(*got_in, m.to(DEV))
+    o.backward(do.to(DEV))
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for name, g, r in zip(NAMES, [o] + [t.grad for t in got_in], [ref_o] + [t.grad for t in ref_in]):
+        assert rel_err(g.detach().float().cpu(), r.detach()) < tol, name
+
+
+def test_leading_batch_dimensions():
+    """Any number of leading batch dimensions, including none, gives the rows of the
+    five-dimensional call."""
+    torch.manual_seed(6)
+    n, h, d = 48, 2, 32
+    q, k, v = (torch.randn(2, 3, h, n, n, d, device=DEV, dtype=torch.bfloat16) for _ in range(3))
+    b = torch.randn(2, 3, h, n, n, device=DEV, dtype=torch.bfloat16)
+    m = torch.rand(2, 3, n, n, device=DEV) < 0.3
+    o = triangle_attention(q, k, v, b, m)
+    assert o.shape == q.shape
+    flat = triangle_attention(q.flatten(0, 1), k.flatten(0, 1), v.flatten(0, 1), b.flatten(0, 1),
+                              m.flatten(0, 1))
+    assert torch.equal(o.flatten(0, 1), flat)
+    single = triangle_attention(q[1, 2], k[1, 2], v[1, 2], b[1, 2], m[1, 2])
+    assert single.shape == q.shape[2:] and torch.equal(single, o[1, 2])

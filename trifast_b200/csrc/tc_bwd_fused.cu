@@ -31,7 +31,6 @@
 // the n keys (the PyTorch semantics, src/trifast/equiv.py:42-69).
 
 #include <math.h>
-#include <stdlib.h>
 
 #include <type_traits>
 
@@ -51,7 +50,7 @@ constexpr int kSmemLimit = 232448;
 constexpr int kRegsIssue = 56, kRegsMath = 224;
 static_assert(256 * kRegsMath + 128 * kRegsIssue <= 384 * 168, "setmaxnreg pool");
 
-template <int D, int NS>
+template <int D, int NS, int SB>
 struct FusedCfg {
   static constexpr int kRowBytes = D * 2;
   static constexpr int kKVBytes = 128 * kRowBytes;       // resident K or V tile
@@ -66,7 +65,11 @@ struct FusedCfg {
   static constexpr int kThreads = 384;
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
   static constexpr int kSbo = 8 * kRowBytes;
-  static constexpr int kDqCol = 192 + 2 * D;             // first dQ column
+  // TMEM columns: SB buffers of S^T [0,64) + dP^T [64,128); then P^T, dS^T (32 each, 16-bit
+  // pairs), dK, dV (D each) and dQ, D columns per 128-query tile
+  static constexpr int kPCol = SB * 128, kDsCol = kPCol + 32, kDkCol = kPCol + 64,
+                       kDvCol = kDkCol + D;
+  static constexpr int kDqCol = kDvCol + D;              // first dQ column
   static constexpr int kMaxJTiles = (512 - kDqCol) / D;  // 128-query tiles whose dQ fits
   static constexpr int kTilesPerGroup = (kMaxJTiles + 1) / 2;
   static int smem_bytes() { return 1024 + 1024 + kTilesBytes; }
@@ -92,7 +95,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <typename T, int D, int NS, int X>
+template <typename T, int D, int NS, int SB, int X>
 __global__ void __launch_bounds__(384, 1)
 tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
@@ -100,7 +103,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                const __grid_constant__ CUtensorMap map_delta, View5 dq, View5 dk, View5 dv,
                const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits_lin,
                int mask_words, Dims dm, FusedGrid grid, unsigned int* status) {
-  using Cfg = FusedCfg<D, NS>;
+  using Cfg = FusedCfg<D, NS, SB>;
   // Barriers.  The per-step ones exist once per step parity (index g & 1, phase
   // (g >> 1) & 1), which leaves every waiter a whole step of slack before a parity
   // could be mistaken for the one two steps earlier.
@@ -239,9 +242,12 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           const int kvb = ktg & 1;
           for (int js = 0; js < njs; ++js, ++g) {
             const int s = g % NS;
+            // the S / dP buffer of this step was last read at step g - SB
+            const int gp = g - SB;
             ok = (js > 0 || mbar_wait_spin(bar(KV_FULL + kvb), (ktg >> 1) & 1, abort_flag)) &&
-                 mbar_wait_spin2(bar(FULL + s), (g / NS) & 1, g > 0, bar(S_FREE + ((g - 1) & 1)),
-                                 ((g - 1) >> 1) & 1, abort_flag);
+                 mbar_wait_spin2(bar(FULL + s), (g / NS) & 1, gp >= 0, bar(S_FREE + (gp & 1)),
+                                 (gp >> 1) & 1, abort_flag);
+            const uint32_t t_s = tmem_base + (g % SB) * 128;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -255,10 +261,10 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
               // descriptor's address field (16-byte units)
 #pragma unroll
               for (int kk = 0; kk < D / 16; ++kk)
-                umma_ss(tmem_base, ak + 2 * kk, bq + 2 * kk, idesc_s, kk > 0);
+                umma_ss(t_s, ak + 2 * kk, bq + 2 * kk, idesc_s, kk > 0);
 #pragma unroll
               for (int kk = 0; kk < D / 16; ++kk)
-                umma_ss(tmem_base + 64, av + 2 * kk, bg + 2 * kk, idesc_s, kk > 0);
+                umma_ss(t_s + 64, av + 2 * kk, bg + 2 * kk, idesc_s, kk > 0);
               umma_commit(bar(S_FULL + (g & 1)));
             }
             __syncwarp();
@@ -296,10 +302,10 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
               if (!(X & 32)) {
 #pragma unroll
                 for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO, dK += dS^T Q, interleaved
-                  umma_ts(tmem_base + 192 + D, tmem_base + 128 + ks * 8, b_do + ks * kStep16Rows,
-                          idesc_acc, (ks > 0) ? 1u : acc);
-                  umma_ts(tmem_base + 192, tmem_base + 160 + ks * 8, b_q + ks * kStep16Rows,
-                          idesc_acc, (ks > 0) ? 1u : acc);
+                  umma_ts(tmem_base + Cfg::kDvCol, tmem_base + Cfg::kPCol + ks * 8,
+                          b_do + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
+                  umma_ts(tmem_base + Cfg::kDkCol, tmem_base + Cfg::kDsCol + ks * 8,
+                          b_q + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
                 }
               }
               umma_commit(bar(ACC_DONE + (g & 1)));
@@ -365,9 +371,9 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       // of the step's 64 queries each.
       const int half = warp >> 2, wq = warp & 3, t = tid & 127;
       const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-      const uint32_t tS = tmem_base + lane_base + half * 32;
-      const uint32_t tDP = tS + 64, tP = tmem_base + lane_base + 128 + half * 16, tDS = tP + 32;
-      const uint32_t tAcc = tmem_base + lane_base + 192 + half * D;  // dK (half 0) or dV (half 1)
+      const uint32_t tS0 = tmem_base + lane_base + half * 32;
+      const uint32_t tP = tmem_base + lane_base + Cfg::kPCol + half * 16, tDS = tP + 32;
+      const uint32_t tAcc = tmem_base + lane_base + Cfg::kDkCol + half * D;  // dK (half 0) or dV (half 1)
       const uint32_t tDQ = tmem_base + lane_base + Cfg::kDqCol;
       const float c1 = dm.scale * kLog2e;
       const float uniform = 1.f / (float)n;
@@ -416,8 +422,9 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
               tc_fence_after();
               if (tid == 0 || tid == 128) TRACE(0, gg, 1);
               float x[32], g_[32];
+              const uint32_t tS = tS0 + (gg % SB) * 128;
               tmem_ld32(tS, reinterpret_cast<uint32_t*>(x));
-              tmem_ld32(tDP, reinterpret_cast<uint32_t*>(g_));
+              tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(g_));
               tmem_wait_ld();
               if (tid == 0 || tid == 128) TRACE(0, gg, 2);
               tc_fence_before();
@@ -603,9 +610,9 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   }
 }
 
-template <typename T, int D, int NS, int X = 0>
+template <typename T, int D, int NS, int SB, int X = 0>
 cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
-  using Cfg = FusedCfg<D, NS>;
+  using Cfg = FusedCfg<D, NS, SB>;
   static_assert(Cfg::kTilesBytes + 2048 <= kSmemLimit, "shared memory");
   const Dims& dm = a.dm;
   const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -642,7 +649,7 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
       return cudaErrorInvalidValue;
   }
   const int smem = Cfg::smem_bytes();
-  auto kern = tc_dqkv_kernel<T, D, NS, X>;
+  auto kern = tc_dqkv_kernel<T, D, NS, SB, X>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   FusedGrid grid;
@@ -663,22 +670,30 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-// The whole row's dQ must fit in TMEM next to the other accumulators.
+// The whole row's dQ must fit in TMEM next to the other accumulators; when it leaves
+// 128 columns free, S^T / dP^T get a second buffer (the MMAs of step g + 1 are then
+// issued while step g is still being read).
 bool tc_bwd_fused_supported(const BwdArgs& a) {
   const int d = a.dm.d;
   if (d != 32 && d != 64) return false;
   if (!a.bias_t || !a.neg_lse2 || !a.maskbits_lin) return false;
   const int njt = (a.dm.n + 127) / 128;
-  const int max_tiles = (d == 32) ? FusedCfg<32, 4>::kMaxJTiles : FusedCfg<64, 2>::kMaxJTiles;
+  const int max_tiles = (d == 32) ? FusedCfg<32, 4, 1>::kMaxJTiles : FusedCfg<64, 2, 1>::kMaxJTiles;
   return njt <= max_tiles;
 }
 
 cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
   if (!tc_bwd_fused_supported(a)) return cudaErrorInvalidValue;
-  if (a.dm.d == 32)
-    return bf16 ? launch_fused<__nv_bfloat16, 32, 4>(a, s) : launch_fused<__half, 32, 4>(a, s);
-  return bf16 ? launch_fused<__nv_bfloat16, 64, 2>(a, s) : launch_fused<__half, 64, 2>(a, s);
+  const int njt = (a.dm.n + 127) / 128;
+  if (a.dm.d == 32) {
+    if (njt <= FusedCfg<32, 4, 2>::kMaxJTiles)
+      return bf16 ? launch_fused<__nv_bfloat16, 32, 4, 2>(a, s) : launch_fused<__half, 32, 4, 2>(a, s);
+    return bf16 ? launch_fused<__nv_bfloat16, 32, 4, 1>(a, s) : launch_fused<__half, 32, 4, 1>(a, s);
+  }
+  if (njt <= FusedCfg<64, 2, 2>::kMaxJTiles)
+    return bf16 ? launch_fused<__nv_bfloat16, 64, 2, 2>(a, s) : launch_fused<__half, 64, 2, 2>(a, s);
+  return bf16 ? launch_fused<__nv_bfloat16, 64, 2, 1>(a, s) : launch_fused<__half, 64, 2, 1>(a, s);
 }
 
 #ifdef TRIFAST_TRACE

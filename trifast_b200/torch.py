@@ -175,11 +175,40 @@ _triangle_attention.register_autograd(_backward, setup_context=_setup_context)
 
 def triangle_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: torch.Tensor,
                        mask: torch.Tensor) -> torch.Tensor:
-    """Fused triangle self-attention.
+    """Fused triangle self-attention (around the starting node).
 
-    q, k, v: (batch, heads, n, n, d); b (pair bias): (batch, heads, n, n), shared
-    by all rows; mask: (batch, n, n) bool, True = key masked out for that row.
-    Returns o with the shape and dtype of q.  Differentiable in q, k, v and b.
+    q, k, v: (*batch, heads, n, n, d); b (pair bias): (*batch, heads, n, n), shared
+    by all rows; mask: (*batch, n, n) bool, True = key masked out for that row.
+    ``*batch`` is any number of leading dimensions, including none (the reference
+    takes exactly one, src/trifast/torch.py:29 notes the rest as to do); they are
+    folded into one batch dimension for the kernels.  Returns o with the shape and
+    dtype of q.  Differentiable in q, k, v and b.
     """
-    o, _ = _triangle_attention(q, k, v, b, mask)
-    return o
+    if q.dim() == 5:
+        o, _ = _triangle_attention(q, k, v, b, mask)
+        return o
+    if q.dim() < 4:
+        raise ValueError(f"q must be (*batch, heads, n, n, d); got {tuple(q.shape)}")
+    lead = q.shape[:-4]
+    if k.shape != q.shape or v.shape != q.shape or b.shape[:-3] != lead or mask.shape[:-2] != lead:
+        raise ValueError("q, k, v, bias and mask must share their leading batch dimensions")
+    fold = lambda t, keep: t.reshape((-1,) + tuple(t.shape[-keep:]))
+    o, _ = _triangle_attention(fold(q, 4), fold(k, 4), fold(v, 4), fold(b, 3), fold(mask, 2))
+    return o.reshape(q.shape)
+
+
+def triangle_attention_ending_node(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                   b: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """Triangle self-attention around the ending node:
+
+        o[i, j] = sum_k softmax_k(q[i, j] . k[k, j] / sqrt(d) + b[k, i] + mask[k, j]) v[k, j]
+
+    (keys run along the first pair index).  It is the starting-node operator on the
+    pair-transposed problem, o = T(triangle_attention(T(q), T(k), T(v), b^T, mask^T)), with T
+    the swap of the two pair dimensions; the transposed q, k, v are read through their
+    strides, nothing is copied but the small bias and mask.  The reference lists this
+    variant as planned (README.md:104 there); shapes and dtypes as in triangle_attention.
+    """
+    t = lambda x: x.transpose(-3, -2)
+    o = triangle_attention(t(q), t(k), t(v), b.transpose(-1, -2), mask.transpose(-1, -2))
+    return t(o)
