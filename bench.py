@@ -234,7 +234,8 @@ class DirectStep:
         self.m8 = m.view(torch.uint8)
         self.o = torch.empty_like(q)
         self.lse = torch.empty((bs, h, rows, n), dtype=torch.float32, device=dev)
-        self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype)
+        self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype,
+                                     flags=_lib.FLAG_SHARE_GPU if group_size > 1 else None)
         self.fws_bytes = self.lib.trifast_forward_workspace_bytes(C.byref(self.shape))
         self.fws = torch.empty(self.fws_bytes, dtype=torch.uint8, device=dev) if self.fws_bytes else None
         if w.backward:
@@ -345,10 +346,15 @@ def run_native(args, w):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # the db all-reduce runs beside the dq/dk/dv kernels, which leave 8 SMs free for it
+        os.environ.setdefault("NCCL_MAX_CTAS", "8")
         dist.init_process_group("nccl", device_id=dev)
     from trifast_b200.dist import shard_rows, triangle_attention_row_sharded
     rows = shard_rows(w.n, rank, world)
-    q, k, v, b, m, do = make_inputs(w, seed=0, rows=rows if world > 1 else None, device=dev)
+    if args.rows and world == 1:
+        rows = slice(0, min(args.rows, w.n))
+    q, k, v, b, m, do = make_inputs(w, seed=0, rows=rows if (world > 1 or args.rows) else None,
+                                    device=dev)
     torch.cuda.synchronize()
     step = DirectStep(w, q, k, v, b, m, do, world)
 
@@ -374,6 +380,14 @@ def run_native(args, w):
         ms = float(t)
     rc = step.lib.trifast_check_device_status(step.stream)
     step._lib.check(rc, "device status after the timed region")
+
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"profiling_aid": True, "rows": q.shape[2], "ms_per_step": ms,
+                              "plan": step.plan, "clocks": clocks}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- the same step through the public operator (allocations, dispatch, autograd) ----
     from trifast_b200 import triangle_attention
@@ -575,6 +589,12 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="metric_n1024", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="profiling aid: only this many pair rows of the workload (a row shard on "
+                         "one GPU; the printed line is then not the benchmark)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="profiling aid: only the kernels-only leg (no host-resident, operator or "
+                         "CPU legs)")
     ap.add_argument("--e2e-chunk-rows", type=int, default=64,
                     help="pair rows per block of the host-resident pipeline (e2e figure)")
     args = ap.parse_args()

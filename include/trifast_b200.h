@@ -70,7 +70,11 @@ typedef enum trifast_kernel {
  * reference's TRIFAST_FORCE_TUNE switch (src/trifast/autotune_helpers.py:12-14):
  * a way to make a non-default kernel run, for A/B measurements and tests. */
 typedef enum trifast_flags {
-  TRIFAST_FLAG_SPLIT_BWD = 1 /* dq and dk/dv as two kernels even where the one-pass kernel fits */
+  TRIFAST_FLAG_SPLIT_BWD = 1, /* dq and dk/dv as two kernels even where the one-pass kernel fits */
+  /* Not a debug switch: set by row-sharded callers.  trifast_backward_dqkv then leaves 8 SMs
+   * free, so that the all-reduce of db launched beside it (another stream) finds room to run
+   * at once instead of after it.  (No reference counterpart: the reference is single-GPU.) */
+  TRIFAST_FLAG_SHARE_GPU = 2
 } trifast_flags;
 
 /* Problem extents, shared by every call. */

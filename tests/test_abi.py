@@ -164,7 +164,7 @@ def test_fused_backward_choice(n, d, dtype, flags, fused):
 
 
 def test_unknown_flag_bits_are_rejected():
-    shp = _lib.make_shape(1, 4, 256, 256, 32, torch.bfloat16, flags=2)
+    shp = _lib.make_shape(1, 4, 256, 256, 32, torch.bfloat16, flags=4)
     assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(_lib.Plan())) == -10
 
 

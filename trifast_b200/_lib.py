@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtrifast_b200.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
-FLAG_SPLIT_BWD = 1                # trifast_flags of the header
+FLAG_SPLIT_BWD, FLAG_SHARE_GPU = 1, 2   # trifast_flags of the header
 STATIC_SCRATCH_BYTES = 16 << 20   # TRIFAST_STATIC_SCRATCH_BYTES of the header
 _KERNEL_ENV = {"": 0, "auto": 0, "simt": 1, "tcgen05": 2}
 

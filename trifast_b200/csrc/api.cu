@@ -15,6 +15,10 @@ namespace {
 __device__ unsigned int g_device_status;  // OR of DeviceStatusBits
 
 constexpr int kMaxDevices = 64;
+// SMs the persistent dq / dk / dv kernels leave free under TRIFAST_FLAG_SHARE_GPU: their
+// CTAs take a whole SM each (registers, shared memory), so a collective kernel launched
+// beside them would otherwise only start when they end.
+constexpr int kSharedGpuSms = 8;
 unsigned int* g_status_ptr[kMaxDevices];
 int g_arch_major[kMaxDevices];
 std::once_flag g_once[kMaxDevices];
@@ -56,7 +60,7 @@ int check_shape(const trifast_shape* s) {
   if (s->dtype < TRIFAST_F32 || s->dtype > TRIFAST_F16) return TRIFAST_ERR_DTYPE;
   if (s->kernel < TRIFAST_KERNEL_AUTO || s->kernel > TRIFAST_KERNEL_TCGEN05)
     return TRIFAST_ERR_KERNEL_CHOICE;
-  if (s->flags & ~TRIFAST_FLAG_SPLIT_BWD) return TRIFAST_ERR_KERNEL_CHOICE;
+  if (s->flags & ~(TRIFAST_FLAG_SPLIT_BWD | TRIFAST_FLAG_SHARE_GPU)) return TRIFAST_ERR_KERNEL_CHOICE;
   return TRIFAST_OK;
 }
 
@@ -270,6 +274,7 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->splits = c.plan.db_row_splits;
   a->dm = c.dm;
   a->dtype = shape->dtype;
+  a->reserve_sms = (shape->flags & TRIFAST_FLAG_SHARE_GPU) ? kSharedGpuSms : 0;
   a->status = c.status;
   return TRIFAST_OK;
 }

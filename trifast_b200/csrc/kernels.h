@@ -41,6 +41,7 @@ struct BwdArgs {
   int splits;
   Dims dm;
   int dtype;
+  int reserve_sms;       // SMs the persistent dq / dk / dv kernels leave free (a collective running beside them)
   unsigned int* status;
 };
 

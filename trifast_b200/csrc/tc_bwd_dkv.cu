@@ -506,6 +506,7 @@ cudaError_t launch_dkv(const BwdArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
+  sms = sms - a.reserve_sms > 0 ? sms - a.reserve_sms : 1;
   const int grid = items.total < sms ? items.total : sms;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dk, a.dv,
                                               a.rowfull, a.mask, dm, items, a.status);

@@ -500,7 +500,7 @@ cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
   items.njt = (dm.n + kBJ - 1) / kBJ;
   items.nrp = (dm.n_rows + 1) / 2;
   items.total = items.njt * items.nrp * dm.batch * dm.heads;
-  const int sms = sm_count_dq();
+  const int sms = sm_count_dq() - a.reserve_sms > 0 ? sm_count_dq() - a.reserve_sms : 1;
   const int grid = items.total < sms ? items.total : sms;
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mbias, a.dq, a.lse, a.delta,
                                               a.rowfull, a.maskbits, a.mask_words, dm, items, a.status);

@@ -661,6 +661,7 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
+  sms = sms - a.reserve_sms > 0 ? sms - a.reserve_sms : 1;
   const int ctas = grid.total < sms ? grid.total : sms;
   kern<<<ctas, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dq, a.dk, a.dv,
                                               a.rowfull, a.maskbits_lin, a.mask_words, dm, grid,

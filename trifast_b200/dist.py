@@ -41,9 +41,14 @@ class CudaKernels:
     def forward(self, q, k, v, b, mask):
         return _triangle_attention(q, k, v, b, mask)
 
+    def __init__(self, share_gpu: bool = False):
+        # under a process group the all-reduce of db runs beside the dq/dk/dv kernels:
+        # they then leave a few SMs free for it (TRIFAST_FLAG_SHARE_GPU)
+        self.flags = _lib.flags_choice() | (_lib.FLAG_SHARE_GPU if share_gpu else 0)
+
     def _common(self, do, q, k, v, b, mask):
         bs, h, n_rows, n, d = _check_inputs(q, k, v, b, mask)
-        shp = _lib.make_shape(bs, h, n, n_rows, d, q.dtype)
+        shp = _lib.make_shape(bs, h, n, n_rows, d, q.dtype, flags=self.flags)
         t = [_prep5(x) for x in (do, q, k, v)]
         return shp, t, _prep4(b), _prep_mask(mask), (bs, h, n_rows, n, d)
 
@@ -126,4 +131,6 @@ def triangle_attention_row_sharded(q, k, v, b, mask, group=None, kernels=None):
     every rank; mask: (batch, local_rows, n).  Returns o for the local rows.  In
     the backward, b.grad is the bias gradient summed over all ranks' rows.
     """
-    return _RowSharded.apply(q, k, v, b, mask, group, kernels or CudaKernels())
+    if kernels is None:
+        kernels = CudaKernels(share_gpu=dist.is_initialized() and dist.get_world_size(group) > 1)
+    return _RowSharded.apply(q, k, v, b, mask, group, kernels)
