@@ -116,7 +116,7 @@ typedef struct trifast_plan {
   int32_t stages;        /* K/V/bias pipeline depth */
   int32_t db_row_splits; /* row groups whose db partials are summed in fixed order */
   int32_t bwd_fused;     /* 1: dq, dk, dv come from one kernel (one exponential per score) */
-  int32_t reserved;
+  int32_t bwd_chunks;    /* query chunks a row is walked in by that kernel (1: dQ of a row fits TMEM) */
 } trifast_plan;
 
 /* Library version as major*10000 + minor*100 + patch. */

@@ -147,20 +147,32 @@ def test_cpu_tensors_are_rejected():
 
 
 # ---------------------------------------------------------------- debug flags, plan.bwd_fused
-@pytest.mark.parametrize("n,d,dtype,flags,fused", [
-    (1024, 32, torch.bfloat16, 0, 1),    # 8 query tiles x 32 columns of dQ = 256: fits
-    (1025, 32, torch.bfloat16, 0, 0),    # a ninth tile does not
-    (2048, 32, torch.bfloat16, 0, 0),
-    (384, 64, torch.float16, 0, 1),      # 3 x 64 columns next to dK, dV of 64 each
-    (512, 64, torch.float16, 0, 0),
-    (1024, 32, torch.bfloat16, _lib.FLAG_SPLIT_BWD, 0),   # forced two-kernel backward
-    (256, 32, torch.float32, 0, 0),      # CUDA-core path has no fused kernel
+@pytest.mark.parametrize("n,d,dtype,flags,fused,chunks", [
+    (1024, 32, torch.bfloat16, 0, 1, 1),    # 8 query tiles x 32 columns of dQ = 256: one chunk
+    (1025, 32, torch.bfloat16, 0, 1, 2),    # a ninth tile: the row is walked in two query chunks
+    (2048, 32, torch.bfloat16, 0, 1, 2),
+    (4096, 32, torch.bfloat16, 0, 1, 4),
+    (384, 64, torch.float16, 0, 1, 1),      # 3 x 64 columns next to dK, dV of 64 each
+    (512, 64, torch.float16, 0, 1, 2),
+    (1024, 64, torch.float16, 0, 1, 3),
+    (1024, 32, torch.bfloat16, _lib.FLAG_SPLIT_BWD, 0, 0),   # forced two-kernel backward
+    (256, 32, torch.float32, 0, 0, 0),      # CUDA-core path has no one-pass kernel
 ])
-def test_fused_backward_choice(n, d, dtype, flags, fused):
+def test_fused_backward_choice(n, d, dtype, flags, fused, chunks):
     plan = _lib.Plan()
     shp = _lib.make_shape(1, 4, n, n, d, dtype, flags=flags)
     assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == 0
-    assert plan.bwd_fused == fused
+    assert (plan.bwd_fused, plan.bwd_chunks) == (fused, chunks)
+
+
+def test_chunked_backward_adds_its_scratch_to_the_workspace():
+    """Rows walked in several query chunks keep fp32 dK / dV partials per CTA:
+    160 CTAs x ceil(n / 128) x 128 keys x 2 d floats."""
+    lib = _lib.load()
+    one = _lib.make_shape(1, 4, 2048, 64, 32, torch.bfloat16, flags=_lib.FLAG_SPLIT_BWD)
+    two = _lib.make_shape(1, 4, 2048, 64, 32, torch.bfloat16)
+    extra = lib.trifast_backward_workspace_bytes(C.byref(two)) - lib.trifast_backward_workspace_bytes(C.byref(one))
+    assert extra == 160 * 2048 * 2 * 32 * 4
 
 
 def test_unknown_flag_bits_are_rejected():

@@ -67,6 +67,11 @@ FUSED_SHAPES = [  # (n, h, d, dtype, mask, rows): every shape the one-pass kerne
     (384, 1, 64, torch.float16, "padding", None),     # largest n for head dim 64
     (1000, 2, 32, torch.bfloat16, "random", 40),      # a row shard of a long problem
     (1024, 1, 32, torch.bfloat16, "none", 150),       # all eight dQ tiles, > 1 item per CTA
+    (1100, 1, 32, torch.bfloat16, "random", 20),      # two query chunks (8 + 1 tiles): dK / dV partials
+    (2048, 1, 32, torch.bfloat16, "padding", 24),     # two full chunks, fully masked rows
+    (512, 1, 64, torch.float16, "random", 16),        # head dim 64: chunks of three tiles (3 + 1)
+    (1001, 1, 64, torch.bfloat16, "padding", 12),     # three chunks (3 + 3 + 2), ragged n
+    (2500, 1, 32, torch.bfloat16, "random", 170),     # three chunks, more items than CTAs
 ]
 
 
@@ -82,7 +87,15 @@ def test_one_pass_backward_equals_two_kernel_backward(n, h, d, dtype, mask, rows
     split = _run_abi(args, flags=_lib.FLAG_SPLIT_BWD)
     for name, a, b in zip(NAMES, fused, split):
         assert not torch.isnan(a.float()).any(), f"{name}: output not fully written"
-        assert torch.equal(a, b), f"{name}: one-pass and two-kernel results differ"
+        if plan["bwd_chunks"] > 1 and name in ("dk", "dv"):
+            # a row walked in query chunks sums dK / dV per chunk and adds the fp32 partials:
+            # another summation order than one accumulation over all queries, so the
+            # 16-bit results may differ in the last place of a few elements
+            err = float((a.float() - b.float()).abs().max())
+            assert err <= 2.0 ** -7 * float(b.float().abs().max()), f"{name}: {err:.3e}"
+            assert float((a != b).float().mean()) < 0.02, name
+        else:
+            assert torch.equal(a, b), f"{name}: one-pass and two-kernel results differ"
 
 
 def test_one_pass_backward_is_run_to_run_deterministic():

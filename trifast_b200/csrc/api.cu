@@ -118,7 +118,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // Carve-up of the backward workspace.
 struct Workspace {
   size_t delta_off, nlse_off, rowfull_off, maskbits_off, db_off, bias_t_off, bias_pad_off,
-      partial_off, total;
+      partial_off, kv_scratch_off, kv_scratch_bytes, total;
   int mask_words;
   bool has_bias_t, has_bias_pad;
 };
@@ -175,6 +175,10 @@ Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   if (w.has_bias_pad) off = align_up(off + bias_copy, 256);
   w.partial_off = off;
   if (plan.db_row_splits > 1) off = align_up(off + dbb * plan.db_row_splits, 256);
+  // dK / dV partials of the one-pass backward for rows walked in several query chunks
+  w.kv_scratch_off = off;
+  w.kv_scratch_bytes = plan.bwd_fused ? tc_bwd_fused_scratch_bytes(s->n, s->d) : 0;
+  off = align_up(off + w.kv_scratch_bytes, 256);
   w.total = off;
   return w;
 }
@@ -215,10 +219,11 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   int splits = 1;
   while (splits < 16 && tiles * splits < want && s->n_rows / (splits * 2) >= 8) splits *= 2;
   p->db_row_splits = splits;
-  // dq, dk, dv from one kernel when the dQ of a whole row (D fp32 columns per 128
-  // queries) fits in TMEM beside the other accumulators (192 + 2 D columns)
-  const int64_t dq_cols = (int64_t)((s->n + 127) / 128) * s->d;
-  p->bwd_fused = (tc_db && dq_cols <= 512 - 192 - 2 * s->d && !(s->flags & TRIFAST_FLAG_SPLIT_BWD)) ? 1 : 0;
+  // dq, dk, dv from one kernel on the tensor-core path; a row whose dQ (D fp32 columns
+  // per 128 queries) does not fit in TMEM beside the other accumulators (192 + 2 D
+  // columns) is walked in bwd_chunks query chunks
+  p->bwd_fused = (tc_db && !(s->flags & TRIFAST_FLAG_SPLIT_BWD)) ? 1 : 0;
+  p->bwd_chunks = p->bwd_fused ? tc_bwd_fused_chunks(s->n, s->d) : 0;
   return TRIFAST_OK;
 }
 
@@ -271,6 +276,7 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->mask_words = w.mask_words;
   a->db_f32 = (float*)(base + w.db_off);
   a->db_partials = (float*)(base + w.partial_off);
+  a->kv_scratch = w.kv_scratch_bytes ? (float*)(base + w.kv_scratch_off) : nullptr;
   a->splits = c.plan.db_row_splits;
   a->dm = c.dm;
   a->dtype = shape->dtype;

@@ -41,6 +41,7 @@ struct BwdArgs {
   int splits;
   Dims dm;
   int dtype;
+  float* kv_scratch;     // per-CTA fp32 dK / dV partials of rows walked in several query chunks, or null
   int reserve_sms;       // SMs the persistent dq / dk / dv kernels leave free (a collective running beside them)
   unsigned int* status;
 };
@@ -63,8 +64,10 @@ bool tc_backward_supported(const BwdArgs& a);
 cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s);
 cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s);
 cudaError_t tc_bwd_db(const BwdArgs& a, cudaStream_t s);
-// dq, dk and dv in one pass over the scores, when a whole row's dQ fits in TMEM
+// dq, dk and dv in one pass over the scores
 bool tc_bwd_fused_supported(const BwdArgs& a);
+int tc_bwd_fused_chunks(int n, int d);             // query chunks per row (1: dQ of a row fits TMEM)
+size_t tc_bwd_fused_scratch_bytes(int n, int d);   // 0 when one chunk
 cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s);
 
 // One warp whose bounded wait runs out after limit_cycles (test support).

@@ -24,8 +24,12 @@
 // MMAs, warp 11 the dQ MMAs: one thread can issue an MMA only every ~60 cycles
 // whatever its size, and no kind queues behind a wait of another.  TMEM columns: S^T [0,64), dP^T [64,128), P^T [128,160),
 // dS^T [160,192) (16-bit pairs), dK [192,192+D), dV [192+D,192+2D), dQ from 192+2D,
-// D columns per 128-query tile: the row fits when ceil(n/128) * D <= 320 - 2D
-// (d = 32: n <= 1024; d = 64: n <= 384); longer rows use the two-kernel path.
+// D columns per 128-query tile: a row fits when ceil(n/128) * D <= 320 - 2D
+// (d = 32: n <= 1024; d = 64: n <= 384).  A longer row is walked in query chunks of as
+// many tiles as fit: per chunk all key tiles are swept again (S, P, dS of a chunk's
+// queries are still evaluated once), dQ of the chunk leaves at its end, and dK / dV of
+// a key tile are completed over the chunks: the partial of the earlier chunks waits as
+// fp32 in a per-CTA scratch (written and read by the same thread, L2-resident).
 //
 // Masked keys weigh exactly zero; rows whose keys are all masked use P = 1/n over
 // the n keys (the PyTorch semantics, src/trifast/equiv.py:42-69).
@@ -44,6 +48,7 @@ using namespace tc;
 constexpr int kBKeys = 128, kBJ = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSmemLimit = 232448;
+constexpr int kFusedMaxCtas = 160;  // grid cap: the per-CTA dK / dV scratch is sized by it
 // Register hand-over (setmaxnreg): 384 threads launch with 168 registers each; what
 // the math warpgroups gain must not exceed what the issue warpgroup releases, or
 // the request blocks forever.
@@ -80,29 +85,23 @@ struct FusedGrid {
   int nkt;       // key tiles of 128
   int njs;       // query steps of 64
   int njt;       // query tiles of 128 (dQ tiles)
+  int nch;       // query chunks: a row whose dQ does not fit TMEM is walked chunk by chunk
+  int jsc;       // query steps per full chunk (even)
 };
-
-#ifdef TRIFAST_TRACE
-// Development aid (not part of the library build): clock stamps of CTA 0.
-__device__ long long g_trace[3][256][8];
-#define TRACE(role, g, slot) \
-  do { if (blockIdx.x == 0 && (g) < 256) g_trace[role][g][slot] = clock64(); } while (0)
-#else
-#define TRACE(role, g, slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <typename T, int D, int NS, int SB, int X>
+template <typename T, int D, int NS, int SB>
 __global__ void __launch_bounds__(384, 1)
 tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                const __grid_constant__ CUtensorMap map_bt, const __grid_constant__ CUtensorMap map_lse,
                const __grid_constant__ CUtensorMap map_delta, View5 dq, View5 dk, View5 dv,
                const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits_lin,
-               int mask_words, Dims dm, FusedGrid grid, unsigned int* status) {
+               int mask_words, Dims dm, FusedGrid grid, float* __restrict__ kv_scratch,
+               unsigned int* status) {
   using Cfg = FusedCfg<D, NS, SB>;
   // Barriers.  The per-step ones exist once per step parity (index g & 1, phase
   // (g >> 1) & 1), which leaves every waiter a whole step of slack before a parity
@@ -121,7 +120,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + 260);
 
   const int n = dm.n;
-  const int nkt = grid.nkt, njs = grid.njs, njt = grid.njt;
+  const int nkt = grid.nkt, njs = grid.njs, njt = grid.njt, nch = grid.nch, jsc = grid.jsc;
   constexpr uint32_t tiles_off = 1024;
   constexpr uint32_t stages_off = tiles_off + 4 * Cfg::kKVBytes;
   constexpr uint32_t pairs_off = stages_off + NS * Cfg::kStageBytes;
@@ -200,6 +199,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       bool ok = true;
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
         const Item im = decode(w);
+        for (int c = 0; c < nch && ok; ++c) {
+        const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
         for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
           if (ktg >= 2)
@@ -211,7 +212,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             tma_load_5d(k_tile(kvb), &map_k, bar(KV_FULL + kvb), 0, kt * kBKeys, im.i, im.h, im.b);
             tma_load_5d(v_tile(kvb), &map_v, bar(KV_FULL + kvb), 0, kt * kBKeys, im.i, im.h, im.b);
           }
-          for (int js = 0; js < njs; ++js, ++g) {
+          for (int js = js0; js < js1; ++js, ++g) {
             const int s = g % NS;
             if (g >= NS)
               ok = __all_sync(0xffffffffu,
@@ -229,6 +230,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             __syncwarp();
           }
         }
+        }
       }
     } else if (warp == 9) {
       // ------------------------------------------------------------ S^T / dP^T issuer
@@ -238,20 +240,21 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       int g = 0, ktg = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        for (int c = 0; c < nch && ok; ++c) {
+        const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
         for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
-          for (int js = 0; js < njs; ++js, ++g) {
+          for (int js = js0; js < js1; ++js, ++g) {
             const int s = g % NS;
             // the S / dP buffer of this step was last read at step g - SB
             const int gp = g - SB;
-            ok = (js > 0 || mbar_wait_spin(bar(KV_FULL + kvb), (ktg >> 1) & 1, abort_flag)) &&
+            ok = (js > js0 || mbar_wait_spin(bar(KV_FULL + kvb), (ktg >> 1) & 1, abort_flag)) &&
                  mbar_wait_spin2(bar(FULL + s), (g / NS) & 1, gp >= 0, bar(S_FREE + (gp & 1)),
                                  (gp >> 1) & 1, abort_flag);
             const uint32_t t_s = tmem_base + (g % SB) * 128;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            TRACE(1, g, 0);
             const uint64_t ak = make_smem_desc(k_tile(kvb), 16, Cfg::kSbo, Cfg::kSwz);
             const uint64_t bq = make_smem_desc(q_tile(s), 16, Cfg::kSbo, Cfg::kSwz);
             const uint64_t av = make_smem_desc(v_tile(kvb), 16, Cfg::kSbo, Cfg::kSwz);
@@ -268,8 +271,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
               umma_commit(bar(S_FULL + (g & 1)));
             }
             __syncwarp();
-            TRACE(1, g, 1);
           }
+        }
         }
       }
     } else if (warp == 10) {
@@ -282,38 +285,37 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       int g = 0, ktg = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        for (int c = 0; c < nch && ok; ++c) {
+        const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
         for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
-          for (int js = 0; js < njs; ++js, ++g) {
+          for (int js = js0; js < js1; ++js, ++g) {
             const int s = g % NS;
             // the first accumulating MMAs of a key tile overwrite dK, dV: the epilogue
             // of the previous key tile must have read them (tested together with
             // P_READY: each test costs a shared-memory round trip)
-            const bool first = js == 0 && ktg > 0;
+            const bool first = js == js0 && ktg > 0;
             ok = mbar_wait_spin2(bar(P_READY + (g & 1)), (g >> 1) & 1, first, bar(ACC_FREE),
                                  (ktg - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            TRACE(2, g, 0);
-            const uint32_t acc = (js > 0) ? 1u : 0u;
+            const uint32_t acc = (js > js0) ? 1u : 0u;
             const uint64_t b_do = make_smem_desc(do_tile(s), Cfg::kSbo, Cfg::kSbo, Cfg::kSwz);
             const uint64_t b_q = make_smem_desc(q_tile(s), Cfg::kSbo, Cfg::kSbo, Cfg::kSwz);
             if (leader) {
-              if (!(X & 32)) {
 #pragma unroll
-                for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO, dK += dS^T Q, interleaved
-                  umma_ts(tmem_base + Cfg::kDvCol, tmem_base + Cfg::kPCol + ks * 8,
-                          b_do + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
-                  umma_ts(tmem_base + Cfg::kDkCol, tmem_base + Cfg::kDsCol + ks * 8,
-                          b_q + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
-                }
+              for (int ks = 0; ks < kBJ / 16; ++ks) {  // dV += P^T dO, dK += dS^T Q, interleaved
+                umma_ts(tmem_base + Cfg::kDvCol, tmem_base + Cfg::kPCol + ks * 8,
+                        b_do + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
+                umma_ts(tmem_base + Cfg::kDkCol, tmem_base + Cfg::kDsCol + ks * 8,
+                        b_q + ks * kStep16Rows, idesc_acc, (ks > 0) ? 1u : acc);
               }
               umma_commit(bar(ACC_DONE + (g & 1)));
               umma_commit(bar(EMPTY + s));
             }
             __syncwarp();
-            TRACE(2, g, 1);
           }
+        }
         }
       }
     } else {
@@ -322,23 +324,24 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
       constexpr uint32_t idesc_dq = make_idesc(128, D, kBf16, true, true);
       constexpr uint32_t kStep16Rows = (16 * Cfg::kRowBytes) >> 4;
-      int g = 0, ktg = 0, pgc = 0, it = 0;
+      int g = 0, ktg = 0, pgc = 0, chg = 0;  // chg: running chunk counter (DQ_FREE phases)
       bool ok = true;
-      for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x, ++it) {
+      for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        for (int c = 0; c < nch && ok; ++c, ++chg) {
+        const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
         for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
-          for (int js = 0; js < njs; ++js, ++g) {
-            const bool with_dq = !(X & 2) && ((js & 1) || js == njs - 1);
-            const int pr = js >> 1, pb = (pgc + pr) & 1;
-            // the first dQ MMA of a row overwrites dQ: the previous row's epilogue must
+          for (int js = js0; js < js1; ++js, ++g) {
+            const bool with_dq = ((js - js0) & 1) || js == js1 - 1;
+            const int pr = (js - js0) >> 1, pb = (pgc + pr) & 1;
+            // the first dQ MMA of a chunk overwrites dQ: the previous chunk's epilogue must
             // have read it
-            const bool first = with_dq && kt == 0 && pr == 0 && it > 0;
+            const bool first = with_dq && kt == 0 && pr == 0 && chg > 0;
             ok = mbar_wait_spin2(bar(P_READY + (g & 1)), (g >> 1) & 1, first, bar(DQ_FREE),
-                                 (it - 1) & 1, abort_flag);
+                                 (chg - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            TRACE(2, g, 2);
             // dS tile of the pair (rows = keys, 128-byte rows of 64 queries, two halves):
             // read as an MN-major A operand it is dS (queries x keys)
             const uint64_t a_ds = make_smem_desc(base + pair_off(pb), Cfg::kHalfBytes, 1024, kSwizzle128);
@@ -354,12 +357,12 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                           b_k + ks * kStep16Rows, idesc_dq, (kt > 0 || ks > 0) ? 1u : 0u);
               }
               umma_commit(bar(ACC_DONE + (g & 1)));
-              if (js == njs - 1) umma_commit(bar(KV_EMPTY + kvb));  // last read of this K, V
+              if (js == js1 - 1) umma_commit(bar(KV_EMPTY + kvb));  // last read of this K, V
             }
             __syncwarp();
-            TRACE(2, g, 3);
           }
-          pgc += (njs + 1) >> 1;
+          pgc += (js1 - js0 + 1) >> 1;
+        }
         }
       }
     }
@@ -388,6 +391,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         // fully masked row only the keys beyond n): word kt * 4 + wq covers this warp's
         // 32 keys of key tile kt, fetched one key tile ahead
         const uint32_t* mrow = maskbits_lin + ((int64_t)b * dm.n_rows + i) * mask_words;
+        for (int c = 0; c < nch && ok; ++c) {
+        const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
         uint32_t mword_next = __ldg(mrow + wq);
 
         for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
@@ -406,10 +411,9 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           const int g0 = g;
           auto query_loop = [&](auto mode_tag) {
             constexpr int kMode = decltype(mode_tag)::value;
-            for (int js = 0; js < njs; ++js) {
-              const int gg = g0 + js;
+            for (int js = js0; js < js1; ++js) {
+              const int gg = g0 + (js - js0);
               const int s = gg % NS;
-              if (tid == 0 || tid == 128) TRACE(0, gg, 0);
               // S^T / dP^T of this step and its bias / lse / delta stage (implied by
               // S_FULL, whose MMAs read Q from the same stage): tested together, each
               // test being a shared-memory round trip.  The waits poll instead of
@@ -420,18 +424,15 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                                               bar(FULL + s), (gg / NS) & 1, abort_flag));
               if (!ok) break;
               tc_fence_after();
-              if (tid == 0 || tid == 128) TRACE(0, gg, 1);
               float x[32], g_[32];
               const uint32_t tS = tS0 + (gg % SB) * 128;
               tmem_ld32(tS, reinterpret_cast<uint32_t*>(x));
               tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(g_));
               tmem_wait_ld();
-              if (tid == 0 || tid == 128) TRACE(0, gg, 2);
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(bar(S_FREE + (gg & 1)));
 
-              if (tid == 0 || tid == 128) TRACE(0, gg, 3);
               // One fused pass per 8 queries: bias^T / lse / delta loads, unpack, FMAs, the
               // exponential, dS and both 16-bit packs; the dS chunk also goes to the
               // shared-memory tile (row = key, 128-byte rows, 16-byte chunks swizzled by
@@ -443,13 +444,13 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 const uint8_t* brow = gbase + bias_off(s) + t * 128;
                 const float4* lse4 = reinterpret_cast<const float4*>(gbase + lse_off(s)) + half * 8;
                 const float4* del4 = reinterpret_cast<const float4*>(gbase + delta_off(s)) + half * 8;
-                uint8_t* srow = gbase + pair_off((pgc + (js >> 1)) & 1) + (js & 1) * Cfg::kHalfBytes +
-                                t * 128;
+                uint8_t* srow = gbase + pair_off((pgc + ((js - js0) >> 1)) & 1) +
+                                ((js - js0) & 1) * Cfg::kHalfBytes + t * 128;
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) {
                   const int chunk = (((half * 4 + q8) ^ (t & 7)) << 4);
-                  const float4 da = (X & 4) ? make_float4(0.f, 0.f, 0.f, 0.f) : del4[q8 * 2];
-                  const float4 db = (X & 4) ? make_float4(0.f, 0.f, 0.f, 0.f) : del4[q8 * 2 + 1];
+                  const float4 da = del4[q8 * 2];
+                  const float4 db = del4[q8 * 2 + 1];
                   const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
                   float p[8];
                   if (kMode == 2) {
@@ -459,10 +460,9 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 8; ++e) p[e] = uniform;
                   } else {
-                    const uint4 u = (X & 8) ? make_uint4(0u, 0u, 0u, 0u)
-                                            : *reinterpret_cast<const uint4*>(brow + chunk);
-                    const float4 la = (X & 4) ? make_float4(-9.f, -9.f, -9.f, -9.f) : lse4[q8 * 2];
-                    const float4 lb = (X & 4) ? make_float4(-9.f, -9.f, -9.f, -9.f) : lse4[q8 * 2 + 1];
+                    const uint4 u = *reinterpret_cast<const uint4*>(brow + chunk);
+                    const float4 la = lse4[q8 * 2];
+                    const float4 lb = lse4[q8 * 2 + 1];
                     const float nl[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
                     float bv[8];
                     unpack2<T>(u.x, bv[0], bv[1]);
@@ -475,15 +475,15 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                       float t0, t1, a0, a1;
                       ffma2(t0, t1, bv[e], bv[e + 1], kLog2e, kLog2e, nl[e], nl[e + 1]);
                       ffma2(a0, a1, x[q8 * 8 + e], x[q8 * 8 + e + 1], c1, c1, t0, t1);
-                      p[e] = (X & 16) ? a0 : ex2(a0);
-                      p[e + 1] = (X & 16) ? a1 : ex2(a1);
+                      p[e] = ex2(a0);
+                      p[e + 1] = ex2(a1);
                     }
                   }
 #pragma unroll
                   for (int e = 0; e < 8; e += 2) {
-                    const int c = q8 * 8 + e;
+                    const int col = q8 * 8 + e;
                     float s0, s1, d0, d1;
-                    ffma2(s0, s1, dl[e], dl[e + 1], -1.f, -1.f, g_[c], g_[c + 1]);   // dP - delta
+                    ffma2(s0, s1, dl[e], dl[e + 1], -1.f, -1.f, g_[col], g_[col + 1]);   // dP - delta
                     fmul2(d0, d1, p[e], p[e + 1], s0, s1);
                     uint32_t wp = pack2<T>(p[e], p[e + 1]);
                     uint32_t wd = pack2<T>(d0, d1);
@@ -491,16 +491,14 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                       wp = dropped ? 0u : wp;
                       wd = dropped ? 0u : wd;
                     }
-                    pp[c >> 1] = wp;
-                    pd[c >> 1] = wd;
+                    pp[col >> 1] = wp;
+                    pd[col >> 1] = wd;
                   }
-                  if (!(X & 1))
-                    *reinterpret_cast<uint4*>(srow + chunk) =
-                        make_uint4(pd[q8 * 4 + 0], pd[q8 * 4 + 1], pd[q8 * 4 + 2], pd[q8 * 4 + 3]);
+                  *reinterpret_cast<uint4*>(srow + chunk) =
+                      make_uint4(pd[q8 * 4 + 0], pd[q8 * 4 + 1], pd[q8 * 4 + 2], pd[q8 * 4 + 3]);
                 }
               }
               __syncwarp();
-              if (tid == 0 || tid == 128) TRACE(0, gg, 4);
               if (lane == 0) mbar_arrive(bar(EMPTY + s));  // bias^T, lse, delta consumed by this warp
 
               if (gg >= 1) {  // the accumulating MMAs of the previous step still read P^T, dS^T
@@ -508,14 +506,12 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                                                             ((gg - 1) >> 1) & 1, abort_flag));
                 if (!ok) break;
               }
-              if (tid == 0 || tid == 128) TRACE(0, gg, 5);
               tmem_st16(tP, pp);
               tmem_st16(tDS, pd);
               tmem_wait_st();
               tc_fence_before();
-              if (!(X & 64)) fence_proxy_async_smem();  // the dS rows in shared memory are read by an MMA
+              fence_proxy_async_smem();  // the dS rows in shared memory are read by an MMA
               __syncwarp();
-              if (tid == 0 || tid == 128) TRACE(0, gg, 6);
               if (lane == 0) mbar_arrive(bar(P_READY + (gg & 1)));
             }
           };
@@ -526,8 +522,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             default: query_loop(std::integral_constant<int, 3>{}); break;
           }
           if (!ok) break;
-          g = g0 + njs;
-          pgc += (njs + 1) >> 1;
+          g = g0 + (js1 - js0);
+          pgc += (js1 - js0 + 1) >> 1;
 
           // dK (warps 0-3) and dV (warps 4-7) of this key tile
           {
@@ -538,12 +534,36 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             tc_fence_after();
             uint32_t acc[D];
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) tmem_ld32(tAcc + 32 * c, acc + 32 * c);
+            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tAcc + 32 * cc, acc + 32 * cc);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(ACC_FREE));  // the next key tile may overwrite dK, dV
-            if (key < n) {
+            // A row walked in several query chunks: dK / dV of a key tile are sums over the
+            // chunks.  The partial of the earlier chunks waits, as fp32, in this CTA's own
+            // scratch (the same thread writes and reads a given element; it stays in L2).
+            if (nch > 1) {
+              float4* part = reinterpret_cast<float4*>(
+                  kv_scratch + ((size_t)blockIdx.x * nkt * kBKeys + (size_t)key) * (2 * D) + half * D);
+              if (c > 0) {
+#pragma unroll
+                for (int e = 0; e < D; e += 4) {
+                  const float4 pv = __ldcg(part + (e >> 2));
+                  acc[e + 0] = __float_as_uint(__uint_as_float(acc[e + 0]) + pv.x);
+                  acc[e + 1] = __float_as_uint(__uint_as_float(acc[e + 1]) + pv.y);
+                  acc[e + 2] = __float_as_uint(__uint_as_float(acc[e + 2]) + pv.z);
+                  acc[e + 3] = __float_as_uint(__uint_as_float(acc[e + 3]) + pv.w);
+                }
+              }
+              if (c + 1 < nch) {
+#pragma unroll
+                for (int e = 0; e < D; e += 4)
+                  __stcg(part + (e >> 2),
+                         make_float4(__uint_as_float(acc[e + 0]), __uint_as_float(acc[e + 1]),
+                                     __uint_as_float(acc[e + 2]), __uint_as_float(acc[e + 3])));
+              }
+            }
+            if (key < n && c + 1 == nch) {
               const View5& out = half ? dv : dk;
               const float sc = half ? 1.f : dm.scale;
               T* dst = reinterpret_cast<T*>(out.p) + b * out.sb + h * out.sh + (int64_t)i * out.si +
@@ -562,16 +582,19 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         }
         if (!ok) break;
 
-        // dQ of the row (complete with the last key tile's MMAs, waited for above): warps
-        // 0-3 take the even 128-query tiles, warps 4-7 the odd ones (lane = query)
+        // dQ of the chunk's queries (complete with the last key tile's MMAs, waited for
+        // above): warps 0-3 take the even 128-query tiles, warps 4-7 the odd ones
+        // (lane = query)
         {
           tc_fence_after();
-          for (int jt = half; jt < njt; jt += 2) {
+          const int jt0 = c * Cfg::kMaxJTiles;
+          const int tiles = min(njt - jt0, (js1 - js0 + 1) >> 1);
+          for (int jl = half; jl < tiles; jl += 2) {
             uint32_t acc[D];
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) tmem_ld32(tDQ + jt * D + 32 * c, acc + 32 * c);
+            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tDQ + jl * D + 32 * cc, acc + 32 * cc);
             tmem_wait_ld();
-            const int j = jt * 128 + t;
+            const int j = (jt0 + jl) * 128 + t;
             if (j < n) {
               T* dst = reinterpret_cast<T*>(dq.p) + b * dq.sb + h * dq.sh + (int64_t)i * dq.si +
                        (int64_t)j * dq.sj;
@@ -588,7 +611,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(DQ_FREE));  // the next row's first dQ MMA may overwrite dQ
+          if (lane == 0) mbar_arrive(bar(DQ_FREE));  // the next chunk's first dQ MMA may overwrite dQ
+        }
         }
       }
     }
@@ -610,7 +634,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   }
 }
 
-template <typename T, int D, int NS, int SB, int X = 0>
+template <typename T, int D, int NS, int SB>
 cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
   using Cfg = FusedCfg<D, NS, SB>;
   static_assert(Cfg::kTilesBytes + 2048 <= kSmemLimit, "shared memory");
@@ -649,7 +673,7 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
       return cudaErrorInvalidValue;
   }
   const int smem = Cfg::smem_bytes();
-  auto kern = tc_dqkv_kernel<T, D, NS, SB, X>;
+  auto kern = tc_dqkv_kernel<T, D, NS, SB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   FusedGrid grid;
@@ -657,30 +681,45 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
   grid.nkt = (dm.n + kBKeys - 1) / kBKeys;
   grid.njs = (dm.n + kBJ - 1) / kBJ;
   grid.njt = (dm.n + 127) / 128;
+  grid.jsc = 2 * Cfg::kMaxJTiles;
+  grid.nch = (grid.njt + Cfg::kMaxJTiles - 1) / Cfg::kMaxJTiles;
+  if (grid.nch > 1 && !a.kv_scratch) return cudaErrorInvalidValue;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   sms = sms - a.reserve_sms > 0 ? sms - a.reserve_sms : 1;
+  if (sms > kFusedMaxCtas) sms = kFusedMaxCtas;  // the dK / dV scratch is sized for this many CTAs
   const int ctas = grid.total < sms ? grid.total : sms;
   kern<<<ctas, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dq, a.dk, a.dv,
                                               a.rowfull, a.maskbits_lin, a.mask_words, dm, grid,
-                                              a.status);
+                                              a.kv_scratch, a.status);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-// The whole row's dQ must fit in TMEM next to the other accumulators; when it leaves
-// 128 columns free, S^T / dP^T get a second buffer (the MMAs of step g + 1 are then
-// issued while step g is still being read).
+// Rows whose dQ fits in TMEM next to the other accumulators are walked once; when that
+// leaves 128 columns free, S^T / dP^T get a second buffer.  Longer rows are walked in
+// query chunks of as many 128-query tiles as fit (8 at d = 32, 3 at d = 64), dK / dV
+// being completed over the chunks through the scratch.
 bool tc_bwd_fused_supported(const BwdArgs& a) {
   const int d = a.dm.d;
   if (d != 32 && d != 64) return false;
   if (!a.bias_t || !a.neg_lse2 || !a.maskbits_lin) return false;
-  const int njt = (a.dm.n + 127) / 128;
+  return tc_bwd_fused_chunks(a.dm.n, d) == 1 || a.kv_scratch != nullptr;
+}
+
+int tc_bwd_fused_chunks(int n, int d) {
+  const int njt = (n + 127) / 128;
   const int max_tiles = (d == 32) ? FusedCfg<32, 4, 1>::kMaxJTiles : FusedCfg<64, 2, 1>::kMaxJTiles;
-  return njt <= max_tiles;
+  return (njt + max_tiles - 1) / max_tiles;
+}
+
+size_t tc_bwd_fused_scratch_bytes(int n, int d) {
+  if (tc_bwd_fused_chunks(n, d) <= 1) return 0;
+  const size_t nkt = (n + kBKeys - 1) / kBKeys;
+  return (size_t)kFusedMaxCtas * nkt * kBKeys * 2 * d * sizeof(float);
 }
 
 cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s) {
@@ -696,13 +735,5 @@ cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s) {
     return bf16 ? launch_fused<__nv_bfloat16, 64, 2, 2>(a, s) : launch_fused<__half, 64, 2, 2>(a, s);
   return bf16 ? launch_fused<__nv_bfloat16, 64, 2, 1>(a, s) : launch_fused<__half, 64, 2, 1>(a, s);
 }
-
-#ifdef TRIFAST_TRACE
-}  // namespace trifast
-extern "C" int trifast_trace_read(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, trifast::g_trace, sizeof(trifast::g_trace));
-}
-namespace trifast {
-#endif
 
 }  // namespace trifast
