@@ -224,7 +224,7 @@ def workload_config(w, gpus):
 class DirectStep:
     """fwd (+bwd) through the C ABI with every buffer preallocated."""
 
-    def __init__(self, w, q, k, v, b, m, do, group_size):
+    def __init__(self, w, q, k, v, b, m, do, group_size, db_reduce="nccl"):
         from trifast_b200 import _lib
         self.lib, self._lib = _lib.load(), _lib
         self.w, self.world = w, group_size
@@ -260,6 +260,10 @@ class DirectStep:
             self.launches += 1 + (1 if plan["kernel"] == 2 else 0) + 1 + 1 + \
                 (1 if plan["db_row_splits"] > 1 else 0) + (1 if plan["bwd_fused"] else 2) + 1
         self.exposed = None   # (event after dq/dk/dv, event after the all-reduce wait)
+        self.reducer = None
+        if w.backward and group_size > 1 and db_reduce == "push":
+            from trifast_b200.dist import PushReducer
+            self.reducer = PushReducer(self.db32.numel(), dev)
 
     def forward(self):
         a, B = self.a, C.byref
@@ -285,8 +289,9 @@ class DirectStep:
             C.c_void_p(self.ws.data_ptr()), C.c_size_t(self.ws.numel()), self.stream)
         self._lib.check(rc, "trifast_backward_dqkv")
 
-    def finalize(self):
-        rc = self.lib.trifast_db_finalize(C.byref(self.shape), C.c_void_p(self.db32.data_ptr()),
+    def finalize(self, src=None):
+        src = self.db32 if src is None else src
+        rc = self.lib.trifast_db_finalize(C.byref(self.shape), C.c_void_p(src.data_ptr()),
                                           C.byref(self.adb), self.stream)
         self._lib.check(rc, "trifast_db_finalize")
 
@@ -296,17 +301,23 @@ class DirectStep:
         if not self.w.backward:
             return
         self.backward_db()
-        work = None
+        work, summed = None, None
         if self.world > 1:
-            work = dist.all_reduce(self.db32, async_op=True)
+            if self.reducer is not None:
+                summed = self.reducer.reduce(self.db32)
+            else:
+                work = dist.all_reduce(self.db32, async_op=True)
         self.backward_dqkv()
-        if work is not None:
+        if self.world > 1:
             if self.exposed is not None:
                 self.exposed[0].record()
-            work.wait()
+            if work is not None:
+                work.wait()
+            else:
+                self.reducer.join()
             if self.exposed is not None:
                 self.exposed[1].record()
-        self.finalize()
+        self.finalize(summed)
 
 
 def time_events(fn, iters):
@@ -356,7 +367,7 @@ def run_native(args, w):
     q, k, v, b, m, do = make_inputs(w, seed=0, rows=rows if (world > 1 or args.rows) else None,
                                     device=dev)
     torch.cuda.synchronize()
-    step = DirectStep(w, q, k, v, b, m, do, world)
+    step = DirectStep(w, q, k, v, b, m, do, world, args.db_reduce)
 
     def barrier():
         torch.cuda.synchronize()
@@ -395,7 +406,7 @@ def run_native(args, w):
 
     def api_step():
         if world > 1:
-            o_ = triangle_attention_row_sharded(qa, ka, va, ba, m)
+            o_ = triangle_attention_row_sharded(qa, ka, va, ba, m, db_reduce=args.db_reduce)
         else:
             o_ = triangle_attention(qa, ka, va, ba, m)
         if w.backward:
@@ -497,7 +508,13 @@ def run_native(args, w):
             exp.append(step.exposed[0].elapsed_time(step.exposed[1]))
         step.exposed = None
         phases["allreduce_exposed"] = sum(exp) / len(exp)
-        phases["allreduce_alone"] = time_events(lambda: dist.all_reduce(step.db32), args.steps)
+        if step.reducer is not None:
+            def alone():
+                step.reducer.reduce(step.db32)
+                step.reducer.join()
+            phases["allreduce_alone"] = time_events(alone, args.steps)
+        else:
+            phases["allreduce_alone"] = time_events(lambda: dist.all_reduce(step.db32), args.steps)
         t = torch.tensor([phases[k_] for k_ in sorted(phases)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         phases = {k_: float(x) for k_, x in zip(sorted(phases), t)}
@@ -550,7 +567,9 @@ def run_native(args, w):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": str(w.dtype).replace("torch.", ""),
-            "data": "synthetic", "config": workload_config(w, world),
+            "data": "synthetic",
+            "config": dict(workload_config(w, world),
+                           **({"db_reduce": args.db_reduce} if world > 1 and w.backward else {})),
             "plan": step.plan, "clocks": clocks,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -589,6 +608,9 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="metric_n1024", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--db-reduce", default="nccl", choices=["nccl", "push"],
+                    help="N > 1: how the db partials of the row shards are summed: NCCL all-reduce "
+                         "or the library's own peer-store exchange")
     ap.add_argument("--rows", type=int, default=0,
                     help="profiling aid: only this many pair rows of the workload (a row shard on "
                          "one GPU; the printed line is then not the benchmark)")

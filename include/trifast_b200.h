@@ -198,6 +198,35 @@ int trifast_backward_dqkv(const trifast_shape* shape,
 int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
                         const trifast_t4* db, void* stream);
 
+/* Sum of the fp32 db partials of the row shards of one box by plain stores to peer-mapped
+ * memory, in place of the all-reduce of step 2 above (no collective library in the path,
+ * cross-rank summation order fixed = rank order).  Every rank calls it once per step with
+ * the same `epoch` (1, 2, 3, ...), at about the same time; rank r pushes slice s of its
+ * partial into rank s's staging area, rank s adds the `world` staged slices in rank order
+ * and pushes the reduced slice into every rank's result buffer.  When the kernel ends,
+ * `result[rank]` holds the full sum.  The staging, result and flag areas of ALL ranks must be
+ * mapped into this process (CUDA IPC / symmetric memory; peer access enabled) and are passed
+ * as device pointers valid here; flags (16 words per rank) and counters (2 words, local) start
+ * at zero and are never reset by the caller.  The ranks wait for each other inside the kernel
+ * with a bounded wait (about 2 s): a rank that misses its peers sets the device status word
+ * (trifast_check_device_status) and returns.  No reference counterpart: the reference is
+ * single-GPU (SURVEY of the reference: no distributed code). */
+typedef struct trifast_push_reduce {
+  int32_t rank, world;      /* world <= 8 */
+  int32_t ctas;             /* CTAs to launch; 0 = 8 (it runs beside the dq/dk/dv kernel) */
+  uint32_t epoch;           /* same on every rank, +1 per call, never 0 */
+  int64_t count;            /* fp32 elements of db */
+  const float* partial;     /* this rank's partial sum (any local memory, 16-byte aligned) */
+  uint32_t* counters;       /* this rank's 2 counter words (local) */
+  float* staging[8];        /* rank r's staging area: trifast_db_push_reduce_staging_floats() floats */
+  float* result[8];         /* rank r's result buffer: count floats */
+  uint32_t* flags[8];       /* rank r's 16 flag words */
+} trifast_push_reduce;
+
+size_t trifast_db_push_reduce_staging_floats(int64_t count, int32_t world);
+
+int trifast_db_push_reduce(const trifast_push_reduce* args, void* stream);
+
 /* Reads and clears the per-device status word that kernels set when one of
  * their bounded waits gives up.  Synchronises `stream` first.  Returns
  * TRIFAST_OK or TRIFAST_ERR_DEVICE_TIMEOUT.  (No reference counterpart: Triton

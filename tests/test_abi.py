@@ -279,3 +279,31 @@ def test_static_scratch_capacity(h, d, dtype, n_ok, n_too_large):
     big = _lib.make_shape(1, h, n_too_large, n_too_large, d, dtype)
     assert 0 < lib.trifast_backward_workspace_bytes(C.byref(ok)) <= _lib.STATIC_SCRATCH_BYTES
     assert lib.trifast_backward_workspace_bytes(C.byref(big)) > _lib.STATIC_SCRATCH_BYTES
+
+
+# ---------------------------------------------------------------- push reduce (host-side checks)
+def test_push_reduce_staging_size_and_argument_checks():
+    lib = _lib.load()
+    f = lib.trifast_db_push_reduce_staging_floats
+    assert f(16, 2) == 16 and f(17, 2) == 24          # slices rounded up to 4 floats
+    assert f(4 * 1024 * 1024, 8) == 4 * 1024 * 1024
+    assert f(0, 2) == 0 and f(16, 9) == 0 and f(16, 0) == 0
+    a = _lib.PushReduce()
+    a.rank, a.world, a.ctas, a.epoch, a.count = 0, 2, 8, 1, 1024
+    a.partial, a.counters = 0x1000, 0x2000
+    for r in range(2):
+        a.staging[r], a.result[r], a.flags[r] = 0x10000, 0x20000, 0x30000
+    call = lambda: lib.trifast_db_push_reduce(C.byref(a), None)
+    a.epoch = 0
+    assert call() == -2                               # epochs start at 1
+    a.epoch, a.world = 1, 9
+    assert call() == -2
+    a.world, a.rank = 2, 2
+    assert call() == -2
+    a.rank, a.partial = 0, 0
+    assert call() == -1
+    a.partial = 0x1004
+    assert call() == -6
+    a.partial, a.flags[1] = 0x1000, 0
+    assert call() == -1
+    assert lib.trifast_db_push_reduce(None, None) == -1

@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, n, dtype, out):
+def _worker(rank, world, port, n, dtype, out, db_reduce="nccl"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world,
@@ -38,9 +38,29 @@ def _worker(rank, world, port, n, dtype, out):
         rows = shard_rows(n, rank, world)
         ql, kl, vl = (t[:, :, rows].contiguous().to(dev).requires_grad_(True) for t in (q, k, v))
         bl = b.to(dev).requires_grad_(True)
-        o = triangle_attention_row_sharded(ql, kl, vl, bl, m[:, rows].to(dev))
+        o = triangle_attention_row_sharded(ql, kl, vl, bl, m[:, rows].to(dev), db_reduce=db_reduce)
         o.backward(do[:, :, rows].to(dev))
         torch.cuda.synchronize()
+        if db_reduce == "push":
+            # a second and third step through the same symmetric buffers (epochs 2, 3), and
+            # the NCCL path on the same inputs: two ranks add two numbers, so the sums agree
+            # bit for bit
+            first = bl.grad.clone()
+            for _ in range(2):
+                ql.grad = kl.grad = vl.grad = bl.grad = None
+                o2 = triangle_attention_row_sharded(ql, kl, vl, bl, m[:, rows].to(dev), db_reduce="push")
+                o2.backward(do[:, :, rows].to(dev))
+                torch.cuda.synchronize()
+                assert torch.equal(bl.grad, first), "push reduce is not reproducible across calls"
+            ql.grad = kl.grad = vl.grad = bl.grad = None
+            o3 = triangle_attention_row_sharded(ql, kl, vl, bl, m[:, rows].to(dev), db_reduce="nccl")
+            o3.backward(do[:, :, rows].to(dev))
+            torch.cuda.synchronize()
+            assert torch.equal(bl.grad, first), "push reduce and NCCL all-reduce disagree"
+            from trifast_b200 import _lib
+            import ctypes
+            assert _lib.load().trifast_check_device_status(
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
         # whole problem on this rank's GPU
         qw, kw, vw, bw = (t.to(dev).requires_grad_(True) for t in (q, k, v, b))
         ow = triangle_attention(qw, kw, vw, bw, m.to(dev))
@@ -67,14 +87,15 @@ def _worker(rank, world, port, n, dtype, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n,dtype", [(136, torch.bfloat16), (72, torch.float32)])
-def test_two_gpu_row_shards_match_single_gpu(n, dtype):
+@pytest.mark.parametrize("n,dtype,db_reduce", [(136, torch.bfloat16, "nccl"), (72, torch.float32, "nccl"),
+                                               (200, torch.bfloat16, "push"), (75, torch.float32, "push")])
+def test_two_gpu_row_shards_match_single_gpu(n, dtype, db_reduce):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, dtype, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, dtype, out, db_reduce)) for r in range(2)]
     for p in procs:
         p.start()
     results = [out.get(timeout=300) for _ in range(2)]

@@ -38,6 +38,12 @@ class Mask(C.Structure):
     _fields_ = [("data", C.c_void_p), ("stride", C.c_int64 * 2)]
 
 
+class PushReduce(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("ctas", C.c_int32), ("epoch", C.c_uint32),
+                ("count", C.c_int64), ("partial", C.c_void_p), ("counters", C.c_void_p),
+                ("staging", C.c_void_p * 8), ("result", C.c_void_p * 8), ("flags", C.c_void_p * 8)]
+
+
 class Plan(C.Structure):
     _fields_ = [("kernel", C.c_int32), ("block_j", C.c_int32), ("block_k", C.c_int32),
                 ("rows_per_cta", C.c_int32), ("stages", C.c_int32), ("db_row_splits", C.c_int32),
@@ -66,6 +72,8 @@ SIGNATURES = {
     "trifast_db_finalize": (C.c_int, [_P(Shape), C.c_void_p, _P(T4), C.c_void_p]),
     "trifast_check_device_status": (C.c_int, [C.c_void_p]),
     "trifast_snapshot_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "trifast_db_push_reduce": (C.c_int, [_P(PushReduce), C.c_void_p]),
+    "trifast_db_push_reduce_staging_floats": (C.c_size_t, [C.c_int64, C.c_int32]),
     "trifast_debug_wait_probe": (C.c_int, [C.c_uint32, C.c_void_p]),
     "trifast_backward_static_scratch": (C.c_int, [_P(Shape), _P(T5), _P(T5), _P(T5), _P(T5), _P(T4),
                                                   _P(Mask), _P(T5), C.c_void_p, _P(T5), _P(T5),

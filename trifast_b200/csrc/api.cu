@@ -481,6 +481,30 @@ int trifast_check_device_status(void* stream) {
   return TRIFAST_ERR_DEVICE_TIMEOUT;
 }
 
+size_t trifast_db_push_reduce_staging_floats(int64_t count, int32_t world) {
+  if (count <= 0 || world < 1 || world > 8) return 0;
+  const int64_t slice = ((count + world - 1) / world + 3) / 4 * 4;
+  return (size_t)slice * world;
+}
+
+int trifast_db_push_reduce(const trifast_push_reduce* a, void* stream) {
+  if (!a) return TRIFAST_ERR_NULL;
+  if (a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world || a->count <= 0 ||
+      a->epoch == 0 || a->ctas < 0 || a->ctas > 64)
+    return TRIFAST_ERR_SHAPE;
+  if (!a->partial || !a->counters) return TRIFAST_ERR_NULL;
+  if (((uintptr_t)a->partial) & 15) return TRIFAST_ERR_ALIGN;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->staging[r] || !a->result[r] || !a->flags[r]) return TRIFAST_ERR_NULL;
+    if ((((uintptr_t)a->staging[r]) & 15) || (((uintptr_t)a->result[r]) & 15)) return TRIFAST_ERR_ALIGN;
+  }
+  int dev;
+  unsigned int* status;
+  int rc = device_setup(&dev, &status);
+  if (rc) return rc;
+  return cuda_rc(db_push_reduce(a, status, (cudaStream_t)stream));
+}
+
 int trifast_snapshot_device_status(uint32_t* host_word, void* stream) {
   if (!host_word) return TRIFAST_ERR_NULL;
   int dev;

@@ -68,6 +68,7 @@ enum DeviceStatusBits : unsigned int {
   kStatusTimeoutBwdDkv = 8u,
   kStatusTimeoutBwdFused = 16u,
   kStatusTimeoutProbe = 32u,
+  kStatusTimeoutPushReduce = 64u,
 };
 
 }  // namespace trifast

@@ -70,6 +70,9 @@ int tc_bwd_fused_chunks(int n, int d);             // query chunks per row (1: d
 size_t tc_bwd_fused_scratch_bytes(int n, int d);   // 0 when one chunk
 cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s);
 
+// Sum of the row shards' fp32 db partials by peer stores (db_push_reduce.cu).
+cudaError_t db_push_reduce(const trifast_push_reduce* a, unsigned int* status, cudaStream_t s);
+
 // One warp whose bounded wait runs out after limit_cycles (test support).
 cudaError_t wait_probe(long long limit_cycles, unsigned int* status, cudaStream_t s);
 

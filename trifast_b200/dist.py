@@ -100,12 +100,82 @@ class CudaKernels:
         return db
 
 
+class PushReducer:
+    """The db exchange without a collective library: every rank pushes slices of its fp32
+    partial into the other ranks' memory with plain stores and adds what it received in rank
+    order (``trifast_db_push_reduce`` of the C ABI, csrc/db_push_reduce.cu).
+
+    Holds, per process group and db size, one symmetric allocation (staging area, result
+    buffer, flag words; mapped into every rank of the box through
+    ``torch.distributed._symmetric_memory``), a side stream and the call counter that all
+    ranks advance together.  ``reduce(partial)`` enqueues the exchange on the side stream
+    behind the work already enqueued on the current stream and returns the local result
+    tensor; ``join()`` makes the current stream wait for it.
+    """
+
+    _FLAG_FLOATS = 64          # 16 flag words per rank, padded
+
+    def __init__(self, count: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.lib = _lib.load()
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("the push reduce serves the GPUs of one box (world <= 8)")
+        self.count, self.device = count, torch.device(device)
+        self.staging_floats = int(self.lib.trifast_db_push_reduce_staging_floats(count, self.world))
+        result_floats = (count + 3) // 4 * 4
+        total = self.staging_floats + result_floats + self._FLAG_FLOATS
+        self.buf = symm.empty(total, dtype=torch.float32, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        dist.barrier(self.group)                     # every rank's flags are zero before any push
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._staging = [p for p in ptrs]
+        self._result = [p + 4 * self.staging_floats for p in ptrs]
+        self._flags = [p + 4 * (self.staging_floats + result_floats) for p in ptrs]
+        self.result = self.buf[self.staging_floats:self.staging_floats + count]
+        self.counters = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.epoch = 0
+
+    def reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() == self.count
+        self.epoch += 1
+        a = _lib.PushReduce()
+        a.rank, a.world, a.ctas, a.epoch, a.count = self.rank, self.world, 8, self.epoch, self.count
+        a.partial, a.counters = partial.data_ptr(), self.counters.data_ptr()
+        for r in range(self.world):
+            a.staging[r], a.result[r], a.flags[r] = self._staging[r], self._result[r], self._flags[r]
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        partial.record_stream(self.stream)
+        with torch.cuda.device(self.device):
+            rc = self.lib.trifast_db_push_reduce(C.byref(a), C.c_void_p(self.stream.cuda_stream))
+        _lib.check(rc, "trifast_db_push_reduce")
+        return self.result
+
+    def join(self) -> None:
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+
+_push_reducers: dict = {}
+
+
+def _push_reducer(count, device, group) -> PushReducer:
+    key = (count, torch.device(device).index, id(group))
+    if key not in _push_reducers:
+        _push_reducers[key] = PushReducer(count, device, group)
+    return _push_reducers[key]
+
+
 class _RowSharded(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, b, mask, group, kernels):
+    def forward(ctx, q, k, v, b, mask, group, kernels, db_reduce="nccl"):
         o, lse = kernels.forward(q, k, v, b, mask)
         ctx.save_for_backward(q, k, v, b, mask, o, lse)
-        ctx.group, ctx.kernels = group, kernels
+        ctx.group, ctx.kernels, ctx.db_reduce = group, kernels, db_reduce
         return o
 
     @staticmethod
@@ -113,24 +183,34 @@ class _RowSharded(torch.autograd.Function):
         q, k, v, b, mask, o, lse = ctx.saved_tensors
         kern, group = ctx.kernels, ctx.group
         db_f32, ws = kern.backward_db(do, q, k, v, b, mask, o, lse)
-        work = None
+        work = reducer = None
         if dist.is_initialized() and dist.get_world_size(group) > 1:
             # Enqueued behind the db kernels; runs beside the dq/dk/dv kernels below.
-            work = dist.all_reduce(db_f32, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            if ctx.db_reduce == "push":
+                reducer = _push_reducer(db_f32.numel(), db_f32.device, group)
+                db_f32 = reducer.reduce(db_f32).view(db_f32.shape)
+            else:
+                work = dist.all_reduce(db_f32, op=dist.ReduceOp.SUM, group=group, async_op=True)
         dq, dk, dv = kern.backward_dqkv(do, q, k, v, b, mask, lse, ws)
         if work is not None:
             work.wait()
+        if reducer is not None:
+            reducer.join()
         db = kern.db_finalize(db_f32, b.dtype)
-        return dq, dk, dv, db, None, None, None
+        return dq, dk, dv, db, None, None, None, None
 
 
-def triangle_attention_row_sharded(q, k, v, b, mask, group=None, kernels=None):
+def triangle_attention_row_sharded(q, k, v, b, mask, group=None, kernels=None, db_reduce="nccl"):
     """Triangle attention on this rank's block of pair rows.
 
     q, k, v: (batch, heads, local_rows, n, d); b: (batch, heads, n, n), the same on
     every rank; mask: (batch, local_rows, n).  Returns o for the local rows.  In
-    the backward, b.grad is the bias gradient summed over all ranks' rows.
+    the backward, b.grad is the bias gradient summed over all ranks' rows: by an NCCL
+    all-reduce (``db_reduce="nccl"``) or by the library's own peer-store exchange
+    (``"push"``: the ranks of one box, summation in rank order).
     """
+    if db_reduce not in ("nccl", "push"):
+        raise ValueError("db_reduce must be 'nccl' or 'push'")
     if kernels is None:
         kernels = CudaKernels(share_gpu=dist.is_initialized() and dist.get_world_size(group) > 1)
-    return _RowSharded.apply(q, k, v, b, mask, group, kernels)
+    return _RowSharded.apply(q, k, v, b, mask, group, kernels, db_reduce)
