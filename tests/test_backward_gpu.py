@@ -350,3 +350,59 @@ def test_error_is_within_the_triton_kernels_own_error(dtype, n):
     for name, x, r in zip(NAMES, [o] + [t.grad for t in g], (ref_o,) + tuple(ref_g)):
         err = float((x.detach().double().cpu() - r.double()).abs().max())
         assert err <= bound[name], f"{name}: max abs err {err:.3e} > Triton kernel's {bound[name]:.3e}"
+
+
+def _fuzz_cases(count=24, seed=2024):
+    """Seeded random problems on the tensor-core path: ragged and aligned n up to 700, both
+    head dims and 16-bit dtypes, row shards, and five mask patterns."""
+    g = torch.Generator().manual_seed(seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    cases = []
+    for idx in range(count):
+        d = (32, 64)[r(0, 1)]
+        n = r(128, 700 if d == 32 else 520)
+        if r(0, 3) == 0:
+            n = (n // 64) * 64                      # aligned now and then
+        rows = n if r(0, 2) == 0 else r(1, min(n, 40))
+        cases.append((idx, n, r(1, 3), d, (torch.bfloat16, torch.float16)[r(0, 1)],
+                      ("none", "random", "padding", "sparse", "blocks")[r(0, 4)], min(rows, 48)))
+    return cases
+
+
+@pytest.mark.parametrize("idx,n,h,d,dtype,mask,rows", _fuzz_cases())
+def test_random_problems_against_the_oracle(idx, n, h, d, dtype, mask, rows):
+    """o, dq, dk, dv, db of randomly drawn problems against the fp64 oracle (3 x (pt + eps) rule
+    of the reference), plus exact zeros of dk, dv at dropped keys of partially masked rows."""
+    g = torch.Generator().manual_seed(1000 + idx)
+    q, k, v = ((torch.randn(1, h, rows, n, d, generator=g) * d ** -0.5).to(dtype) for _ in range(3))
+    b = torch.randn(1, h, n, n, generator=g).to(dtype)
+    do = torch.randn(1, h, rows, n, d, generator=g).to(dtype)
+    if mask == "none":
+        m = torch.zeros(1, rows, n, dtype=torch.bool)
+    elif mask == "random":
+        m = torch.rand(1, rows, n, generator=g) < 0.4
+    elif mask == "padding":
+        nv = int(0.7 * n)
+        m = ((torch.arange(rows)[:, None] >= max(1, rows - 3)) | (torch.arange(n)[None, :] >= nv))[None]
+    elif mask == "sparse":                              # almost everything dropped
+        m = torch.rand(1, rows, n, generator=g) < 0.97
+    else:                                               # whole 128-key tiles dropped on some rows
+        m = torch.zeros(1, rows, n, dtype=torch.bool)
+        m[0, ::2, 128:256] = True
+        m[0, 1::3, : min(n, 128)] = True
+    m = m.contiguous()
+    got = tuple(t.float().cpu() for t in _run_abi((q, k, v, b, m, do), kernel=_lib.KERNEL_TCGEN05))
+    f = [t.float() for t in (q, k, v, b)]
+    o, _, grads = orc.forward_backward_chunked(f[0], f[1], f[2], f[3], m, do=do.float(),
+                                               rows_per_chunk=8, acc_dtype=torch.float64)
+    qq, kk, vv, bb = (t.detach().clone().requires_grad_(True) for t in (q, k, v, b))
+    oo = orc.attention_reference_port(qq, kk, vv, bb, m)
+    oo.backward(do)
+    pt = tuple(t.detach().float() for t in (oo, qq.grad, kk.grad, vv.grad, bb.grad))
+    tag = f"fuzz {idx}: n={n} h={h} d={d} {dtype} mask={mask} rows={rows}"
+    for nm, x, r_, p in zip(NAMES, got, (o,) + grads, pt):
+        assert_within_pt_error(x, p, r_, DTYPE_EPS[dtype], f"{tag} {nm}")
+    partial = ~m.all(dim=-1)
+    sel = (m & partial[..., None])[:, None, :, :, None].expand_as(got[2])
+    if sel.any():
+        assert float(got[2][sel].abs().max()) == 0.0 and float(got[3][sel].abs().max()) == 0.0, tag

@@ -439,7 +439,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // running maximum (see kLazyTau)
         const float m_new = (mt > m_run + kLazyTau) ? mt : m_run;
         const float neg = -m_new * kLog2e;
-        const float alpha = ex2(fmaf(m_run, kLog2e, neg));
+        // (difference first: exactly 1 when the maximum stays, also at the initial value,
+        // where a fused m_run * log2e + neg would leave the rounding residue of 1e30 * log2e
+        // in the exponent and turn a key tile with no open key into inf * 0)
+        const float alpha = ex2((m_run - m_new) * kLog2e);
         m_run = m_new;
 
         if (kt > 0) {
