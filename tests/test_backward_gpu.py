@@ -6,6 +6,8 @@ public operator)."""
 
 import ctypes as C
 
+import os
+
 import pytest
 import torch
 
@@ -369,7 +371,8 @@ def _fuzz_cases(count=24, seed=2024):
     return cases
 
 
-@pytest.mark.parametrize("idx,n,h,d,dtype,mask,rows", _fuzz_cases())
+@pytest.mark.parametrize("idx,n,h,d,dtype,mask,rows",
+                         _fuzz_cases(int(os.environ.get("TRIFAST_B200_FUZZ_DRAWS", "24"))))
 def test_random_problems_against_the_oracle(idx, n, h, d, dtype, mask, rows):
     """o, dq, dk, dv, db of randomly drawn problems against the fp64 oracle (3 x (pt + eps) rule
     of the reference), plus exact zeros of dk, dv at dropped keys of partially masked rows."""

@@ -9,6 +9,8 @@ Tolerances
 * masked keys: exactly zero weight (bitwise-identical outputs when masked k/v change).
 """
 
+import os
+
 import pytest
 import torch
 
@@ -299,3 +301,61 @@ def test_weight_updates():
         opt.step()
     for k, p in model.named_parameters():
         assert not torch.equal(before[k], p), f"parameter {k} did not update"
+
+
+def _random_square_cases(count=32, seed=77):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    cases = []
+    for idx in range(count):
+        d = (16, 32, 64, 128)[r(0, 3)]
+        n = r(1, 260) if r(0, 3) else r(1, 24)
+        cases.append((idx, n, r(1, 4), d, r(1, 2), (torch.float32, torch.bfloat16, torch.float16)[r(0, 2)],
+                      ("none", "random", "head", "tail", "sparse")[r(0, 4)], ("dense", "permuted")[r(0, 1)],
+                      (0.5, 1.0, 2.0)[r(0, 2)]))
+    return cases
+
+
+@pytest.mark.parametrize("idx,n,h,d,bs,dtype,mask,layout,std",
+                         _random_square_cases(int(os.environ.get("TRIFAST_B200_FUZZ_DRAWS", "32"))))
+def test_random_square_problems_through_the_public_op(idx, n, h, d, bs, dtype, mask, layout, std):
+    """Seeded random whole problems through `triangle_attention` + autograd (every kernel family:
+    n < 128 and d = 16 / 128 on CUDA cores, the rest on tensor cores), batch 1-2, dense or
+    permuted-projection layouts, masks that drop the head or the tail of the keys, input scale
+    0.5-2 (flat to peaked softmax), against the fp64 oracle."""
+    g = torch.Generator().manual_seed(5000 + idx)
+    if layout == "dense":
+        q, k, v = (torch.randn(bs, h, n, n, d, generator=g) * std for _ in range(3))
+        b = torch.randn(bs, h, n, n, generator=g) * std
+    else:
+        q, k, v = ((torch.randn(bs, n, n, h, d, generator=g) * std).permute(0, 3, 1, 2, 4) for _ in range(3))
+        b = (torch.randn(bs, n, n, h, generator=g) * std).permute(0, 3, 1, 2)
+    q, k, v, b = (t.to(dtype) for t in (q, k, v, b))
+    do = torch.randn(bs, h, n, n, d, generator=g).to(dtype)
+    keys = torch.arange(n)
+    if mask == "none":
+        m = torch.zeros(bs, n, n, dtype=torch.bool)
+    elif mask == "random":
+        m = torch.rand(bs, n, n, generator=g) < 0.5
+    elif mask == "head":                               # the first keys dropped, row by row differently
+        cut = torch.randint(0, n + 1, (bs, n, 1), generator=g)
+        m = keys[None, None, :] < cut
+    elif mask == "tail":
+        cut = torch.randint(0, n + 1, (bs, n, 1), generator=g)
+        m = keys[None, None, :] >= cut
+    else:
+        m = torch.rand(bs, n, n, generator=g) < 0.95
+    m = m.contiguous()
+    got = run_kernel(q, k, v, b, m, do)
+    ref = run_oracle64(q, k, v, b, m, do)
+    tag = f"draw {idx}: n={n} h={h} d={d} bs={bs} {dtype} mask={mask} {layout} std={std}"
+    if dtype == torch.float32:
+        for name, x, r_ in zip(NAMES, got, ref):
+            assert torch.isfinite(x).all(), f"{tag} {name}: not finite"
+            e = rel_err(x, r_)
+            assert e <= FP32_REL_TOL, f"{tag} {name}: rel err {e:.3e}"
+    else:
+        pt = run_pt(q, k, v, b, m, do)
+        for name, x, r_, p in zip(NAMES, got, ref, pt):
+            assert torch.isfinite(x).all(), f"{tag} {name}: not finite"
+            assert_within_pt_error(x, p, r_, DTYPE_EPS[dtype], f"{tag} {name}")
