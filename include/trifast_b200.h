@@ -125,6 +125,11 @@ int trifast_version(void);
 /* Text for a status code (static storage). */
 const char* trifast_status_str(int status);
 
+/* Name of the CUDA error behind the calling thread's most recent TRIFAST_ERR_LAUNCH
+ * ("cudaSuccess" if there was none).  No reference counterpart: the reference raises
+ * the CUDA error through PyTorch. */
+const char* trifast_last_cuda_error(void);
+
 /* Fixed tile heuristic.  Stands in for Autotuner.run of the reference
  * (src/trifast/autotune.py:110-156): same key (n, h, d, dtype), but a table
  * instead of benchmarking and an on-disk cache.  Pure host code. */

@@ -307,3 +307,18 @@ def test_push_reduce_staging_size_and_argument_checks():
     a.partial, a.flags[1] = 0x1000, 0
     assert call() == -1
     assert lib.trifast_db_push_reduce(None, None) == -1
+
+
+def test_extent_one_dimensions_get_canonical_strides():
+    """`contiguous()` keeps whatever strides extent-1 dimensions came with; the pointers and
+    strides handed to the library are the canonical ones."""
+    import torch
+    from trifast_b200.torch import _prep4, _prep5, _prep_mask
+    b = torch.randn(1, 1, 1, 4).permute(0, 3, 1, 2)            # (1, 4, 1, 1), last stride 4
+    assert b.stride(-1) != 1 and b.is_contiguous()
+    pb = _prep4(b)
+    assert pb.stride() == (4, 1, 1, 1) and torch.equal(pb, b)
+    q = torch.randn(1, 1, 1, 3, 16).permute(0, 3, 1, 2, 4)      # extent-1 strides of 48 elements
+    assert _prep5(q).data_ptr() == q.data_ptr()                 # 16-byte multiples: passed as is
+    m = torch.zeros(2, 1, 1, dtype=torch.bool).as_strided((2, 1, 1), (1, 7, 7))
+    assert _prep_mask(m).stride() == (1, 1, 1)

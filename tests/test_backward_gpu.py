@@ -74,6 +74,7 @@ FUSED_SHAPES = [  # (n, h, d, dtype, mask, rows): every shape the one-pass kerne
     (512, 1, 64, torch.float16, "random", 16),        # head dim 64: chunks of three tiles (3 + 1)
     (1001, 1, 64, torch.bfloat16, "padding", 12),     # three chunks (3 + 3 + 2), ragged n
     (2500, 1, 32, torch.bfloat16, "random", 170),     # three chunks, more items than CTAs
+    (141, 2, 32, torch.float16, "random", 1),         # a single pair row of a ragged problem
 ]
 
 

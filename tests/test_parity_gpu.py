@@ -16,7 +16,7 @@ import torch
 
 from oracle import triangle_oracle as orc
 from tests.helpers import (DTYPE_EPS, FP32_REL_TOL, assert_direction, assert_within_pt_error,
-                           golden_cases, load_golden, rel_err)
+                           golden_cases, load_golden, max_abs, rel_err)
 from trifast_b200 import triangle_attention
 from trifast_b200.configs import WORKLOADS, Workload, make_inputs
 from trifast_b200.utils import gen_tensors
@@ -352,7 +352,9 @@ def test_random_square_problems_through_the_public_op(idx, n, h, d, bs, dtype, m
     if dtype == torch.float32:
         for name, x, r_ in zip(NAMES, got, ref):
             assert torch.isfinite(x).all(), f"{tag} {name}: not finite"
-            e = rel_err(x, r_)
+            # (floor on the scale: with one open key per row dq, dk and db are zero in exact
+            # arithmetic and fp32 leaves the rounding of dP - delta, a few 1e-7)
+            e = max_abs(x, r_) / max(float(r_.abs().max()), 1e-2)
             assert e <= FP32_REL_TOL, f"{tag} {name}: rel err {e:.3e}"
     else:
         pt = run_pt(q, k, v, b, m, do)

@@ -55,6 +55,7 @@ _P = C.POINTER
 SIGNATURES = {
     "trifast_version": (C.c_int, []),
     "trifast_status_str": (C.c_char_p, [C.c_int]),
+    "trifast_last_cuda_error": (C.c_char_p, []),
     "trifast_pick_plan": (C.c_int, [_P(Shape), _P(Plan)]),
     "trifast_backward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
     "trifast_forward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
@@ -105,7 +106,8 @@ def status_str(rc: int) -> str:
 
 def check(rc: int, what: str) -> None:
     if rc != 0:
-        raise RuntimeError(f"{what}: {status_str(rc)} (status {rc})")
+        detail = f", {load().trifast_last_cuda_error().decode()}" if rc == -9 else ""   # TRIFAST_ERR_LAUNCH
+        raise RuntimeError(f"{what}: {status_str(rc)} (status {rc}{detail})")
 
 
 # Per-device pinned host word that mirrors the device status word (see

@@ -285,7 +285,14 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   return TRIFAST_OK;
 }
 
-int cuda_rc(cudaError_t e) { return e == cudaSuccess ? TRIFAST_OK : TRIFAST_ERR_LAUNCH; }
+// The CUDA error behind the last TRIFAST_ERR_LAUNCH of the calling thread.
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+
+int cuda_rc(cudaError_t e) {
+  if (e == cudaSuccess) return TRIFAST_OK;
+  g_last_cuda_error = e;
+  return TRIFAST_ERR_LAUNCH;
+}
 
 }  // namespace
 }  // namespace trifast
@@ -295,6 +302,8 @@ using namespace trifast;
 extern "C" {
 
 int trifast_version(void) { return 100; }
+
+const char* trifast_last_cuda_error(void) { return cudaGetErrorName(g_last_cuda_error); }
 
 const char* trifast_status_str(int status) {
   switch (status) {

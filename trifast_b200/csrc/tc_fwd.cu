@@ -642,7 +642,9 @@ static bool encode(CUtensorMap* map, CUtensorMapDataType dt, uint64_t elem_bytes
   for (int i = 0; i + 1 < rank; ++i) {
     uint64_t s = strides_bytes[i];
     // extent-1 dimensions may come with arbitrary strides: give them the dense pitch
-    if (dims[i + 1] == 1) s = (i == 0) ? dims[0] * elem_bytes : gstr[i - 1] * dims[i];
+    // (rounded up to the 16 bytes a stride must be a multiple of; it is never stepped)
+    if (dims[i + 1] == 1)
+      s = (i == 0) ? ((dims[0] * elem_bytes + 15) & ~(uint64_t)15) : gstr[i - 1] * dims[i];
     if (s == 0 || (s & 15)) return false;
     gstr[i] = s;
   }

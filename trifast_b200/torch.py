@@ -29,20 +29,33 @@ def _row_vector_ok(t: torch.Tensor) -> bool:
         and t.stride(-2) >= t.shape[-1]
 
 
+def _dense(t: torch.Tensor) -> torch.Tensor:
+    """A contiguous tensor with the canonical strides.  ``contiguous()`` alone keeps whatever
+    strides the extent-1 dimensions came with (PyTorch ignores them), but the C side reads
+    every stride."""
+    t = t.contiguous()
+    want, acc = [], 1
+    for n in reversed(t.shape):
+        want.append(acc)
+        acc *= max(n, 1)
+    want = tuple(reversed(want))
+    return t if t.stride() == want else t.as_strided(t.shape, want)
+
+
 def _prep5(t):
-    return t if _row_vector_ok(t) else t.contiguous()
+    return t if _row_vector_ok(t) else _dense(t)
 
 
 def _prep4(t):
     return t if (t.stride(-1) == 1 and all(s >= 0 for s in t.stride())
-                 and t.stride(-2) >= t.shape[-1]) else t.contiguous()
+                 and t.stride(-2) >= t.shape[-1]) else _dense(t)
 
 
 def _prep_mask(m):
     if m.dtype != torch.bool:
         raise TypeError("mask must be a bool tensor (True = key masked out)")
     if m.stride(-1) != 1 or m.stride(-2) < m.shape[-1]:
-        m = m.contiguous()
+        m = _dense(m)
     return m.view(torch.uint8)
 
 
