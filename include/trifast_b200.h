@@ -266,8 +266,8 @@ int trifast_debug_wait_probe(uint32_t limit_us, void* stream);
  * TRIFAST_STATIC_SCRATCH_BYTES (16 MiB, reserved on every GPU that loads the
  * library until the process exits); larger problems return
  * TRIFAST_ERR_TOO_LARGE and nothing is launched.  At h = 4 that covers n up to 224
- * for bf16 / fp16 with d = 32 or 64 (where the fp32 row-split partials of db take most
- * of the workspace) and n up to 576 for fp32 or d = 16 / 128; with h = 1, n up to 448.
+ * for bf16 / fp16 with d = 16, 32 or 64 (where the fp32 row-split partials of db take most
+ * of the workspace) and n up to 576 for fp32 or d = 128; with h = 1, n up to 448.
  *
  * The first call on each device resolves the array's device address (that
  * device must be current); make that first call outside any stream capture.

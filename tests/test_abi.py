@@ -50,7 +50,8 @@ def test_version_and_status_strings():
     (100, 4, 32, torch.bfloat16, _lib.KERNEL_SIMT),
     (64, 1, 64, torch.bfloat16, _lib.KERNEL_SIMT),    # below one tile
     (256, 4, 128, torch.bfloat16, _lib.KERNEL_SIMT),
-    (256, 4, 16, torch.float16, _lib.KERNEL_SIMT),
+    (256, 4, 16, torch.float16, _lib.KERNEL_TCGEN05),  # 32-byte rows
+    (64, 4, 16, torch.float16, _lib.KERNEL_SIMT),
 ])
 def test_heuristic_table(n, h, d, dtype, kernel):
     plan = _lib.pick_plan(1, h, n, n, d, dtype)
@@ -267,6 +268,7 @@ def test_expanded_views_are_materialised_by_the_python_layer():
 @pytest.mark.parametrize("h,d,dtype,n_ok,n_too_large", [
     (4, 32, torch.bfloat16, 224, 256),    # tensor-core plan: the row-split db partials dominate
     (4, 64, torch.float16, 224, 256),
+    (4, 16, torch.bfloat16, 224, 256),
     (1, 32, torch.bfloat16, 448, 480),
     (4, 128, torch.bfloat16, 576, 608),   # CUDA-core plan
     (4, 32, torch.float32, 576, 608),

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 from oracle import triangle_oracle as orc
-from tests.helpers import (DTYPE_EPS, abi_backward, abi_forward, assert_direction,
+from tests.helpers import (DTYPE_EPS, abi_backward, abi_forward, assert_direction, max_abs,
                            assert_within_pt_error, rel_err)
 from trifast_b200 import _lib, triangle_attention
 from trifast_b200.configs import WORKLOADS, make_inputs
@@ -356,14 +356,14 @@ def test_error_is_within_the_triton_kernels_own_error(dtype, n):
 
 
 def _fuzz_cases(count=24, seed=2024):
-    """Seeded random problems on the tensor-core path: ragged and aligned n up to 700, both
-    head dims and 16-bit dtypes, row shards, and five mask patterns."""
+    """Seeded random problems on the tensor-core path: ragged and aligned n up to 700, the three
+    head dims and both 16-bit dtypes, row shards, and five mask patterns."""
     g = torch.Generator().manual_seed(seed)
     r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
     cases = []
     for idx in range(count):
-        d = (32, 64)[r(0, 1)]
-        n = r(128, 700 if d == 32 else 520)
+        d = (16, 32, 64)[r(0, 2)]
+        n = r(128, 700 if d <= 32 else 520)
         if r(0, 3) == 0:
             n = (n // 64) * 64                      # aligned now and then
         rows = n if r(0, 2) == 0 else r(1, min(n, 40))
@@ -410,3 +410,35 @@ def test_random_problems_against_the_oracle(idx, n, h, d, dtype, mask, rows):
     sel = (m & partial[..., None])[:, None, :, :, None].expand_as(got[2])
     if sel.any():
         assert float(got[2][sel].abs().max()) == 0.0 and float(got[3][sel].abs().max()) == 0.0, tag
+
+
+HEAD_DIM_16_SHAPES = [  # (n, h, rows, dtype, mask)
+    (128, 1, None, torch.bfloat16, "none"),
+    (333, 2, None, torch.float16, "random"),
+    (512, 2, 40, torch.bfloat16, "padding"),
+    (1024, 1, 24, torch.bfloat16, "random"),     # all eight dQ tiles of one pass
+    (1300, 1, 12, torch.float16, "padding"),     # two query chunks
+]
+
+
+@pytest.mark.parametrize("n,h,rows,dtype,mask", HEAD_DIM_16_SHAPES)
+def test_head_dim_16_on_tensor_cores(n, h, rows, dtype, mask):
+    """d = 16 (32-byte rows, 32-byte swizzle, 16-column accumulators): forward and backward on
+    the tensor-core kernels against the fp64 oracle and against the CUDA-core kernels."""
+    args = _inputs(n, h, 16, dtype, mask, rows)
+    assert _lib.pick_plan(1, h, n, args[0].shape[2], 16, dtype)["kernel"] == _lib.KERNEL_TCGEN05
+    got = tuple(t.float().cpu() for t in _run_abi(args, kernel=_lib.KERNEL_TCGEN05))
+    simt = tuple(t.float().cpu() for t in _run_abi(args, kernel=_lib.KERNEL_SIMT))
+    q, k, v, b, m, do = args
+    f = [t.float() for t in (q, k, v, b)]
+    o, _, grads = orc.forward_backward_chunked(f[0], f[1], f[2], f[3], m, do=do.float(),
+                                               rows_per_chunk=8, acc_dtype=torch.float64)
+    qq, kk, vv, bb = (t.detach().clone().requires_grad_(True) for t in (q, k, v, b))
+    oo = orc.attention_reference_port(qq, kk, vv, bb, m)
+    oo.backward(do)
+    pt = tuple(t.detach().float() for t in (oo, qq.grad, kk.grad, vv.grad, bb.grad))
+    for nm, x, y, r_, p in zip(NAMES, got, simt, (o,) + grads, pt):
+        assert torch.isfinite(x).all(), nm
+        assert_within_pt_error(x, p, r_, DTYPE_EPS[dtype], f"d=16 n={n} {nm}")
+        assert_direction(x, p, r_, f"d=16 n={n} {nm}")
+        assert max_abs(x, y) <= 3 * (max_abs(y, r_) + DTYPE_EPS[dtype]), f"d=16 n={n} {nm} vs CUDA cores"

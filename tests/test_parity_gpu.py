@@ -353,8 +353,9 @@ def test_random_square_problems_through_the_public_op(idx, n, h, d, bs, dtype, m
         for name, x, r_ in zip(NAMES, got, ref):
             assert torch.isfinite(x).all(), f"{tag} {name}: not finite"
             # (floor on the scale: with one open key per row dq, dk and db are zero in exact
-            # arithmetic and fp32 leaves the rounding of dP - delta, a few 1e-7)
-            e = max_abs(x, r_) / max(float(r_.abs().max()), 1e-2)
+            # arithmetic and fp32 leaves the rounding of dP - delta, two sums of d products
+            # of size ~sqrt(d) each)
+            e = max_abs(x, r_) / max(float(r_.abs().max()), 1e-2 * d ** 0.5)
             assert e <= FP32_REL_TOL, f"{tag} {name}: rel err {e:.3e}"
     else:
         pt = run_pt(q, k, v, b, m, do)

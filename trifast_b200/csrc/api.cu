@@ -188,10 +188,12 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   if (rc) return rc;
   *p = trifast_plan{};
   const bool half = s->dtype != TRIFAST_F32;
-  // tcgen05 path: 16-bit inputs, d in {32, 64}; problems smaller than one 128-wide
+  // tcgen05 path: 16-bit inputs, d in {16, 32, 64}; problems smaller than one 128-wide
   // tile gain nothing from it.  (n % 8 != 0 runs on it through a padded bias copy in
-  // the workspace: TMA needs a 16-byte row pitch.)
-  const bool tc_ok = half && (s->d == 32 || s->d == 64) && s->n >= 128;
+  // the workspace: TMA needs a 16-byte row pitch.)  The two-kernel backward has no
+  // d = 16 tiles.
+  const bool tc_ok = half && (s->d == 16 || s->d == 32 || s->d == 64) && s->n >= 128 &&
+                     !(s->d == 16 && (s->flags & TRIFAST_FLAG_SPLIT_BWD));
   int kernel = s->kernel;
   if (kernel == TRIFAST_KERNEL_AUTO) kernel = tc_ok ? TRIFAST_KERNEL_TCGEN05 : TRIFAST_KERNEL_SIMT;
   if (kernel == TRIFAST_KERNEL_TCGEN05 && !tc_ok) return TRIFAST_ERR_KERNEL_CHOICE;
@@ -200,7 +202,7 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
     p->block_j = 128;
     p->block_k = 128;
     p->rows_per_cta = 2;
-    p->stages = (s->d == 32) ? 3 : 2;
+    p->stages = (s->d <= 32) ? 3 : 2;
   } else {
     p->block_j = 64;
     p->block_k = (s->d <= 32) ? 32 : 16;

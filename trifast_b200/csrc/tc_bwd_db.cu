@@ -45,7 +45,7 @@ struct DbCfg {
   static constexpr int kVecBytes = 128 * 4;
   static constexpr int kStageBytes = 4 * kTileBytes + 2 * kVecBytes;   // multiple of 1024
   static constexpr int kThreads = 640;
-  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr uint64_t kSwz = RowSwizzle<D>::kDesc;
   static constexpr int kSbo = 8 * kRowBytes;
   static int smem_bytes() { return 1024 + 1024 + NS * kStageBytes; }
 };
@@ -344,7 +344,7 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
   const uint64_t dims5[5] = {(uint64_t)D, (uint64_t)dm.n, (uint64_t)dm.n_rows, (uint64_t)dm.heads,
                              (uint64_t)dm.batch};
   const uint32_t box[5] = {(uint32_t)D, 128, 1, 1, 1};
-  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  const CUtensorMapSwizzle swz = (CUtensorMapSwizzle)RowSwizzle<D>::kTma;
   auto map5 = [&](CUtensorMap* m, const View5& v) {
     const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
                             (uint64_t)v.sb * eb};
@@ -386,6 +386,8 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
 cudaError_t tc_bwd_db(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
   if (!a.neg_lse2 || !a.maskbits_lin) return cudaErrorInvalidValue;
+  if (a.dm.d == 16)
+    return bf16 ? launch_db<__nv_bfloat16, 16, 4>(a, s) : launch_db<__half, 16, 4>(a, s);
   if (a.dm.d == 32)
     return bf16 ? launch_db<__nv_bfloat16, 32, 4>(a, s) : launch_db<__half, 32, 4>(a, s);
   return bf16 ? launch_db<__nv_bfloat16, 64, 3>(a, s) : launch_db<__half, 64, 3>(a, s);

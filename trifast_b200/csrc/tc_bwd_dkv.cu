@@ -517,6 +517,7 @@ cudaError_t launch_dkv(const BwdArgs& a, cudaStream_t stream) {
 
 cudaError_t tc_bwd_dkv(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
+  if (a.dm.d != 32 && a.dm.d != 64) return cudaErrorInvalidValue;
   static_assert(DkvCfg<32, 2, 4>::kTilesBytes + 2048 <= kSmemLimit, "smem");
   static_assert(DkvCfg<64, 1, 4>::kTilesBytes + 2048 <= kSmemLimit, "smem");
   if (!a.bias_t || !a.neg_lse2) return cudaErrorInvalidValue;

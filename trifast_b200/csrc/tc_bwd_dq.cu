@@ -512,7 +512,7 @@ cudaError_t launch_dq(const BwdArgs& a, cudaStream_t stream) {
 bool tc_backward_supported(const BwdArgs& a) {
   const Dims& dm = a.dm;
   if (a.dtype != TRIFAST_BF16 && a.dtype != TRIFAST_F16) return false;
-  if (dm.d != 32 && dm.d != 64) return false;
+  if (dm.d != 16 && dm.d != 32 && dm.d != 64) return false;  // (d = 16: one-pass kernel only)
   if (dm.n < 128) return false;
   if (!a.maskbits || !a.rowfull || !a.delta || !a.neg_lse2) return false;
   // the bias goes through TMA: 16-byte row pitch, or the padded copy from the workspace
@@ -524,6 +524,7 @@ bool tc_backward_supported(const BwdArgs& a) {
 
 cudaError_t tc_bwd_dq(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
+  if (a.dm.d != 32 && a.dm.d != 64) return cudaErrorInvalidValue;
   if (a.dm.d == 32)
     return bf16 ? launch_dq<__nv_bfloat16, 32, 4>(a, s) : launch_dq<__half, 32, 4>(a, s);
   return bf16 ? launch_dq<__nv_bfloat16, 64, 3>(a, s) : launch_dq<__half, 64, 3>(a, s);

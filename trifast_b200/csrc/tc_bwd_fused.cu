@@ -68,14 +68,16 @@ struct FusedCfg {
   static constexpr int kPairBytes = 2 * kHalfBytes;      // dS of a pair of steps: 128 x 128
   static constexpr int kTilesBytes = 4 * kKVBytes + NS * kStageBytes + 2 * kPairBytes;
   static constexpr int kThreads = 384;
-  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr uint64_t kSwz = RowSwizzle<D>::kDesc;
   static constexpr int kSbo = 8 * kRowBytes;
   // TMEM columns: SB buffers of S^T [0,64) + dP^T [64,128); then P^T, dS^T (32 each, 16-bit
   // pairs), dK, dV (D each) and dQ, D columns per 128-query tile
+  // (an accumulator of D = 16 columns still starts on a multiple of 32 columns)
+  static constexpr int kAcc = D < 32 ? 32 : D;
   static constexpr int kPCol = SB * 128, kDsCol = kPCol + 32, kDkCol = kPCol + 64,
-                       kDvCol = kDkCol + D;
-  static constexpr int kDqCol = kDvCol + D;              // first dQ column
-  static constexpr int kMaxJTiles = (512 - kDqCol) / D;  // 128-query tiles whose dQ fits
+                       kDvCol = kDkCol + kAcc;
+  static constexpr int kDqCol = kDvCol + kAcc;              // first dQ column
+  static constexpr int kMaxJTiles = (512 - kDqCol) / kAcc;  // 128-query tiles whose dQ fits
   static constexpr int kTilesPerGroup = (kMaxJTiles + 1) / 2;
   static int smem_bytes() { return 1024 + 1024 + kTilesBytes; }
 };
@@ -110,7 +112,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 S_FREE = S_FULL + 2, P_READY = S_FREE + 2, ACC_DONE = P_READY + 2,
                 ACC_FREE = ACC_DONE + 2, DQ_FREE = ACC_FREE + 1, NBARS = DQ_FREE + 1;
   static_assert(NBARS * 8 <= 256, "barrier area");
-  static_assert(Cfg::kDqCol + Cfg::kMaxJTiles * D <= 512, "TMEM columns");
+  static_assert(Cfg::kDqCol + Cfg::kMaxJTiles * Cfg::kAcc <= 512, "TMEM columns");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -353,7 +355,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 // beyond n and their dQ rows are never stored)
 #pragma unroll
                 for (int ks = 0; ks < kBKeys / 16; ++ks)
-                  umma_ss(tmem_base + Cfg::kDqCol + pr * D, a_ds + ks * ((16 * 128) >> 4),
+                  umma_ss(tmem_base + Cfg::kDqCol + pr * Cfg::kAcc, a_ds + ks * ((16 * 128) >> 4),
                           b_k + ks * kStep16Rows, idesc_dq, (kt > 0 || ks > 0) ? 1u : 0u);
               }
               umma_commit(bar(ACC_DONE + (g & 1)));
@@ -376,7 +378,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
       const uint32_t tS0 = tmem_base + lane_base + half * 32;
       const uint32_t tP = tmem_base + lane_base + Cfg::kPCol + half * 16, tDS = tP + 32;
-      const uint32_t tAcc = tmem_base + lane_base + Cfg::kDkCol + half * D;  // dK (half 0) or dV (half 1)
+      const uint32_t tAcc = tmem_base + lane_base + Cfg::kDkCol + half * Cfg::kAcc;  // dK (half 0) or dV (half 1)
       const uint32_t tDQ = tmem_base + lane_base + Cfg::kDqCol;
       const float c1 = dm.scale * kLog2e;
       const float uniform = 1.f / (float)n;
@@ -533,8 +535,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
             uint32_t acc[D];
-#pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tAcc + 32 * cc, acc + 32 * cc);
+            tmem_ld_cols<D>(tAcc, acc);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
@@ -591,8 +592,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           const int tiles = min(njt - jt0, (js1 - js0 + 1) >> 1);
           for (int jl = half; jl < tiles; jl += 2) {
             uint32_t acc[D];
-#pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tDQ + jl * D + 32 * cc, acc + 32 * cc);
+            tmem_ld_cols<D>(tDQ + jl * Cfg::kAcc, acc);
             tmem_wait_ld();
             const int j = (jt0 + jl) * 128 + t;
             if (j < n) {
@@ -646,7 +646,7 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
                              (uint64_t)dm.batch};
   const uint32_t box_kv[5] = {(uint32_t)D, 128, 1, 1, 1};
   const uint32_t box_q[5] = {(uint32_t)D, (uint32_t)kBJ, 1, 1, 1};
-  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  const CUtensorMapSwizzle swz = (CUtensorMapSwizzle)RowSwizzle<D>::kTma;
   auto map5 = [&](CUtensorMap* m, const View5& v, const uint32_t* box) {
     const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
                             (uint64_t)v.sb * eb};
@@ -705,14 +705,16 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
 // being completed over the chunks through the scratch.
 bool tc_bwd_fused_supported(const BwdArgs& a) {
   const int d = a.dm.d;
-  if (d != 32 && d != 64) return false;
+  if (d != 16 && d != 32 && d != 64) return false;
   if (!a.bias_t || !a.neg_lse2 || !a.maskbits_lin) return false;
   return tc_bwd_fused_chunks(a.dm.n, d) == 1 || a.kv_scratch != nullptr;
 }
 
 int tc_bwd_fused_chunks(int n, int d) {
   const int njt = (n + 127) / 128;
-  const int max_tiles = (d == 32) ? FusedCfg<32, 4, 1>::kMaxJTiles : FusedCfg<64, 2, 1>::kMaxJTiles;
+  const int max_tiles = (d == 16)   ? FusedCfg<16, 4, 1>::kMaxJTiles
+                        : (d == 32) ? FusedCfg<32, 4, 1>::kMaxJTiles
+                                    : FusedCfg<64, 2, 1>::kMaxJTiles;
   return (njt + max_tiles - 1) / max_tiles;
 }
 
@@ -726,6 +728,11 @@ cudaError_t tc_bwd_dqkv_fused(const BwdArgs& a, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
   if (!tc_bwd_fused_supported(a)) return cudaErrorInvalidValue;
   const int njt = (a.dm.n + 127) / 128;
+  if (a.dm.d == 16) {
+    if (njt <= FusedCfg<16, 4, 2>::kMaxJTiles)
+      return bf16 ? launch_fused<__nv_bfloat16, 16, 4, 2>(a, s) : launch_fused<__half, 16, 4, 2>(a, s);
+    return bf16 ? launch_fused<__nv_bfloat16, 16, 4, 1>(a, s) : launch_fused<__half, 16, 4, 1>(a, s);
+  }
   if (a.dm.d == 32) {
     if (njt <= FusedCfg<32, 4, 2>::kMaxJTiles)
       return bf16 ? launch_fused<__nv_bfloat16, 32, 4, 2>(a, s) : launch_fused<__half, 32, 4, 2>(a, s);

@@ -243,11 +243,30 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// N consecutive columns (16, or a multiple of 32) of this thread's lane.
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  static_assert(N == 16 || N % 32 == 0, "column count");
+  if constexpr (N == 16) {
+    tmem_ld16(taddr, r);
+  } else {
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) tmem_ld32(taddr + 32 * c, r + 32 * c);
+  }
+}
+
 // ------------------------------------------------------------------ UMMA
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in bits [0,14),
 // leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46),
 // descriptor version 1 in [46,48), swizzle mode in [61,64).
 enum Swizzle : uint64_t { kSwizzleNone = 0, kSwizzle128 = 2, kSwizzle64 = 4, kSwizzle32 = 6 };
+// Tiles of 128 rows x D 16-bit elements: the swizzle span equals the row (32, 64 or 128
+// bytes), both in the shared-memory descriptors and in the tensor maps.
+template <int D> struct RowSwizzle {
+  static_assert(D == 16 || D == 32 || D == 64, "head dim of the tensor-core tiles");
+  static constexpr uint64_t kDesc = D == 16 ? kSwizzle32 : D == 32 ? kSwizzle64 : kSwizzle128;
+  static constexpr int kTma = D == 16 ? 1 : D == 32 ? 2 : 3;   // CU_TENSOR_MAP_SWIZZLE_32B / 64B / 128B
+};
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
                                                    uint32_t sbo_bytes, uint64_t swizzle) {

@@ -74,7 +74,7 @@ struct FwdCfg {
   static constexpr int kStageBytes = 2 * R * kTileBytes + kBiasBytes;
   static constexpr int kTilesBytes = R * kTileBytes + NS * kStageBytes;
   static constexpr int kThreads = R * 128 + 128;
-  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;
+  static constexpr uint64_t kSwz = RowSwizzle<D>::kDesc;
   static constexpr int kSbo = 8 * kRowBytes;              // pitch of 8-row groups
   // per slot: 4 mask words per 128-key chunk, one or two buffers (this item's and the next's)
   static int mask_bytes(int n, int bufs) { return bufs * R * ((n + kBK - 1) / kBK) * 16; }
@@ -451,14 +451,23 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           if (!ok) break;
           tc_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t acc[32];
-              tmem_ld32(tO + 32 * c, acc);
+            if constexpr (D == 16) {
+              uint32_t acc[16];
+              tmem_ld16(tO, acc);
               tmem_wait_ld();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-              tmem_st32(tO + 32 * c, acc);
+              for (int e = 0; e < 16; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+              tmem_st16(tO, acc);
+            } else {
+#pragma unroll
+              for (int c = 0; c < D / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld32(tO + 32 * c, acc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                tmem_st32(tO + 32 * c, acc);
+              }
             }
           }
         }
@@ -513,8 +522,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const float inv = 1.f / l_run;
       T* dst = reinterpret_cast<T*>(o.p) + b * o.sb + h * o.sh + (int64_t)i * o.si + (int64_t)j * o.sj;
       uint32_t acc[D];
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) tmem_ld32(tO + 32 * c, acc + 32 * c);
+      tmem_ld_cols<D>(tO, acc);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
@@ -577,7 +585,7 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
   const uint64_t dims5[5] = {(uint64_t)D, (uint64_t)dm.n, (uint64_t)dm.n_rows, (uint64_t)dm.heads,
                              (uint64_t)dm.batch};
   const uint32_t box5[5] = {(uint32_t)D, 128, 1, 1, 1};
-  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  const CUtensorMapSwizzle swz = (CUtensorMapSwizzle)RowSwizzle<D>::kTma;
   auto map5 = [&](CUtensorMap* m, const View5& v) {
     const uint64_t st[4] = {(uint64_t)v.sj * eb, (uint64_t)v.si * eb, (uint64_t)v.sh * eb,
                             (uint64_t)v.sb * eb};
@@ -670,9 +678,11 @@ bool make_tensor_map_f32(CUtensorMap* map, int rank, void* base, const uint64_t*
 
 bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
   if (dtype != TRIFAST_BF16 && dtype != TRIFAST_F16) return false;
-  if (dm.d != 32 && dm.d != 64) return false;
+  if (dm.d != 16 && dm.d != 32 && dm.d != 64) return false;
   if (dm.n < 128) return false;
-  const int smem = (dm.d == 32) ? FwdCfg<32, 2, 3>::smem_bytes(dm.n) : FwdCfg<64, 2, 2>::smem_bytes(dm.n);
+  const int smem = (dm.d == 16)   ? FwdCfg<16, 2, 3>::smem_bytes(dm.n)
+                   : (dm.d == 32) ? FwdCfg<32, 2, 3>::smem_bytes(dm.n)
+                                  : FwdCfg<64, 2, 2>::smem_bytes(dm.n);
   if (smem > kSmemLimit) return false;
   if (a) {
     if (((uintptr_t)a->o.p) & 15 || (a->o.sj * 2) % 16) return false;
@@ -691,6 +701,8 @@ bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
 
 cudaError_t tc_forward(const FwdArgs& a, const trifast_plan&, cudaStream_t s) {
   const bool bf16 = a.dtype == TRIFAST_BF16;
+  if (a.dm.d == 16)
+    return bf16 ? launch<__nv_bfloat16, 16, 2, 3>(a, s) : launch<__half, 16, 2, 3>(a, s);
   if (a.dm.d == 32)
     return bf16 ? launch<__nv_bfloat16, 32, 2, 3>(a, s) : launch<__half, 32, 2, 3>(a, s);
   return bf16 ? launch<__nv_bfloat16, 64, 2, 2>(a, s) : launch<__half, 64, 2, 2>(a, s);
