@@ -253,9 +253,10 @@ class DirectStep:
             self.adb = L.t4(self.db)
         plan = L.pick_plan(bs, h, n, rows, d, q.dtype)
         self.plan = plan
-        # launches per step: forward 1; backward: row flags + packed mask, bias transpose
-        # (tensor-core path only), delta, db, split reduce (if split), dq, dk/dv, cast
-        self.launches = 1
+        # launches per step: forward 1 (+ the live key-tile ranges of the rows on the tensor-core
+        # path, + the padded bias copy for n % 8 != 0); backward: row flags + packed mask, bias
+        # transpose (tensor-core path only), delta, db, split reduce (if split), dq, dk/dv, cast
+        self.launches = 1 + ((1 + (1 if n % 8 else 0)) if plan["kernel"] == 2 else 0)
         if w.backward:
             self.launches += 1 + (1 if plan["kernel"] == 2 else 0) + 1 + 1 + \
                 (1 if plan["db_row_splits"] > 1 else 0) + (1 if plan["bwd_fused"] else 2) + 1

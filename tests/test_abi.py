@@ -61,13 +61,17 @@ def test_heuristic_table(n, h, d, dtype, kernel):
         assert (plan["block_j"], plan["block_k"]) == (128, 128)
 
 
-def test_forward_workspace_only_for_ragged_n_on_tensor_cores():
+def test_forward_workspace_sizes():
+    """Tensor-core plan: the live key-tile range of every row (4 bytes per row, 256-byte
+    granules); ragged n adds the padded bias copy, packed masks and row flags.  CUDA-core
+    plan: none."""
     lib = _lib.load()
-    for n, want in ((1024, False), (1000, False), (1001, True), (191, True), (100, False)):
-        shp = _lib.make_shape(1, 4, n, n, 32, torch.bfloat16)
-        assert (lib.trifast_forward_workspace_bytes(C.byref(shp)) > 0) == want, n
-    shp = _lib.make_shape(1, 4, 1001, 1001, 32, torch.float32)
-    assert lib.trifast_forward_workspace_bytes(C.byref(shp)) == 0
+    size = lambda n, dtype=torch.bfloat16: lib.trifast_forward_workspace_bytes(
+        C.byref(_lib.make_shape(1, 4, n, n, 32, dtype)))
+    assert size(1024) == 4096 and size(1000) == 4096          # 4 bytes x 1000 rows -> 4096
+    assert size(1001) > 4 * 1001 * 1008 * 2 and size(191) > 4 * 191 * 192 * 2   # + bias copy
+    assert size(100) == 0                                     # below one tile: CUDA cores
+    assert size(1001, torch.float32) == 0
 
 
 def test_heuristic_rejects_impossible_forced_kernel():

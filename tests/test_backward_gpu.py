@@ -442,3 +442,54 @@ def test_head_dim_16_on_tensor_cores(n, h, rows, dtype, mask):
         assert_within_pt_error(x, p, r_, DTYPE_EPS[dtype], f"d=16 n={n} {nm}")
         assert_direction(x, p, r_, f"d=16 n={n} {nm}")
         assert max_abs(x, y) <= 3 * (max_abs(y, r_) + DTYPE_EPS[dtype]), f"d=16 n={n} {nm} vs CUDA cores"
+
+
+@pytest.mark.parametrize("d,dtype", [(32, torch.bfloat16), (64, torch.float16), (16, torch.bfloat16)])
+def test_key_tiles_without_an_open_key_are_skipped_exactly(d, dtype):
+    """Rows whose open keys sit in a sub-range of the 128-key tiles (dropped head, dropped tail,
+    both, a single open key, nothing dropped, everything dropped) next to each other: the
+    kernels walk only each row's live tiles.  Outputs must equal the oracle, dk / dv must be
+    exactly zero at every dropped key (walked or not), and where a two-kernel backward exists
+    (it walks every tile) dq, dk, dv must agree with it bit for bit."""
+    n, h, rows = 640, 2, 24                       # five key tiles
+    q, k, v, b, _, do = _inputs(n, h, d, dtype, "none", rows, seed=11)
+    m = torch.zeros(1, rows, n, dtype=torch.bool)
+    keys = torch.arange(n)
+    for i in range(rows):
+        kind = i % 6
+        if kind == 0:
+            m[0, i] = keys < 128 + 7 * i                     # head dropped: first live tile 1
+        elif kind == 1:
+            m[0, i] = keys >= 300 - i                        # tail dropped: live tiles 0..2
+        elif kind == 2:
+            m[0, i] = (keys < 256) | (keys >= 384)           # only tile 2 live
+        elif kind == 3:
+            m[0, i] = keys != (77 * i) % n                   # a single open key
+        elif kind == 4:
+            m[0, i] = False
+        else:
+            m[0, i] = True                                   # fully masked: all n keys, uniform
+    m = m.contiguous()
+    args = (q, k, v, b, m, do)
+    got = tuple(t.float().cpu() for t in _run_abi(args, kernel=_lib.KERNEL_TCGEN05))
+    f = [t.float() for t in (q, k, v, b)]
+    o, _, grads = orc.forward_backward_chunked(f[0], f[1], f[2], f[3], m, do=do.float(),
+                                               rows_per_chunk=8, acc_dtype=torch.float64)
+    qq, kk, vv, bb = (t.detach().clone().requires_grad_(True) for t in (q, k, v, b))
+    oo = orc.attention_reference_port(qq, kk, vv, bb, m)
+    oo.backward(do)
+    pt = tuple(t.detach().float() for t in (oo, qq.grad, kk.grad, vv.grad, bb.grad))
+    for nm, x, r_, p in zip(NAMES, got, (o,) + grads, pt):
+        assert torch.isfinite(x).all(), nm
+        assert_within_pt_error(x, p, r_, DTYPE_EPS[dtype], f"live tiles d={d} {nm}")
+    partial = ~m.all(dim=-1)
+    sel = (m & partial[..., None])[:, None, :, :, None].expand_as(got[2])
+    assert float(got[2][sel].abs().max()) == 0.0 and float(got[3][sel].abs().max()) == 0.0
+    if d != 16:
+        split = tuple(t.float().cpu() for t in _run_abi(args, kernel=_lib.KERNEL_TCGEN05,
+                                                        flags=_lib.FLAG_SPLIT_BWD))
+        # (a row walked in several query chunks sums dK / dV in another order: o and dq only)
+        one_pass = _lib.pick_plan(1, h, n, rows, d, dtype)["bwd_chunks"] == 1
+        for nm, x, y in zip(NAMES[:4], got[:4], split[:4]):
+            if one_pass or nm in ("o", "dq"):
+                assert torch.equal(x, y), f"{nm}: the walk over live tiles differs from the walk over all"

@@ -117,25 +117,32 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Carve-up of the backward workspace.
 struct Workspace {
-  size_t delta_off, nlse_off, rowfull_off, maskbits_off, db_off, bias_t_off, bias_pad_off,
-      partial_off, kv_scratch_off, kv_scratch_bytes, total;
+  size_t delta_off, nlse_off, rowfull_off, rowrange_off, maskbits_off, db_off, bias_t_off,
+      bias_pad_off, partial_off, kv_scratch_off, kv_scratch_bytes, total;
   int mask_words;
   bool has_bias_t, has_bias_pad;
 };
 
-// Forward workspace: only the tensor-core path with n % 8 != 0 needs one (a copy of
-// the bias with a 16-byte row pitch, the packed key masks and the row flags).
+// Forward workspace of the tensor-core path: the live key-tile range of every row, and for
+// n % 8 != 0 a copy of the bias with a 16-byte row pitch, the packed key masks and the row
+// flags.  The CUDA-core path needs none.
 struct FwdWorkspace {
-  size_t rowfull_off, maskbits_off, bias_pad_off, total;
+  size_t rowrange_off, rowfull_off, maskbits_off, bias_pad_off, total;
   int mask_words;
+  bool ragged;
 };
 
 FwdWorkspace carve_fwd(const trifast_shape* s, const trifast_plan& plan) {
   FwdWorkspace w{};
   w.mask_words = ((s->n + 127) / 128) * 4;
-  if (plan.kernel != TRIFAST_KERNEL_TCGEN05 || s->n % 8 == 0) return w;
-  const size_t n_pad = (size_t)(s->n + 7) / 8 * 8;
+  if (plan.kernel != TRIFAST_KERNEL_TCGEN05) return w;
   size_t off = 0;
+  w.rowrange_off = off;
+  off = (off + (size_t)s->batch * s->n_rows * sizeof(uint32_t) + 255) / 256 * 256;
+  w.total = off;
+  w.ragged = s->n % 8 != 0;
+  if (!w.ragged) return w;
+  const size_t n_pad = (size_t)(s->n + 7) / 8 * 8;
   w.rowfull_off = off;
   off = (off + (size_t)s->batch * s->n_rows + 255) / 256 * 256;
   w.maskbits_off = off;
@@ -159,6 +166,8 @@ Workspace carve(const trifast_shape* s, const trifast_plan& plan) {
   off = align_up(off + stat, 256);
   w.rowfull_off = off;
   off = align_up(off + (size_t)s->batch * s->n_rows, 256);
+  w.rowrange_off = off;
+  off = align_up(off + (size_t)s->batch * s->n_rows * sizeof(uint32_t), 256);
   w.mask_words = ((s->n + 127) / 128) * 4;
   w.maskbits_off = off;
   // two layouts of the packed key masks, one after the other (see BwdArgs)
@@ -273,6 +282,7 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->bias_t = w.has_bias_t ? (void*)(base + w.bias_t_off) : nullptr;
   a->bias_pad = w.has_bias_pad ? (void*)(base + w.bias_pad_off) : nullptr;
   a->rowfull = (uint8_t*)(base + w.rowfull_off);
+  a->rowrange = (uint32_t*)(base + w.rowrange_off);
   a->maskbits = (uint32_t*)(base + w.maskbits_off);
   a->maskbits_lin = a->maskbits + (size_t)shape->batch * shape->n_rows * w.mask_words;
   a->mask_words = w.mask_words;
@@ -372,9 +382,12 @@ int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifa
   a.mask_words = w.mask_words;
   if (w.total) {
     char* base = (char*)workspace;
-    a.rowfull = (uint8_t*)(base + w.rowfull_off);
-    a.maskbits = (uint32_t*)(base + w.maskbits_off);
-    a.bias_pad = (void*)(base + w.bias_pad_off);
+    a.rowrange = (uint32_t*)(base + w.rowrange_off);
+    if (w.ragged) {
+      a.rowfull = (uint8_t*)(base + w.rowfull_off);
+      a.maskbits = (uint32_t*)(base + w.maskbits_off);
+      a.bias_pad = (void*)(base + w.bias_pad_off);
+    }
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (c.plan.kernel == TRIFAST_KERNEL_TCGEN05) {

@@ -15,6 +15,9 @@ struct FwdArgs {
   uint8_t* rowfull;      // (b, n_rows)
   uint32_t* maskbits;    // (b, n_rows, mask_words)
   int mask_words;
+  // (b, n_rows): live key tiles [lo, hi) of each row as lo | hi << 16 (tensor-core path,
+  // every n; null otherwise)
+  uint32_t* rowrange;
   Dims dm;
   int dtype;
   unsigned int* status;  // device status word
@@ -36,6 +39,7 @@ struct BwdArgs {
   // same bits in key order: word w holds, at bit l, key 32 * w + l
   uint32_t* maskbits_lin;
   int mask_words;        // 4 * ceil(n / 128)
+  uint32_t* rowrange;    // (b, n_rows): live key tiles [lo, hi) of the row as lo | hi << 16
   float* db_f32;         // (b, h, n, n) fp32 result of the row reduction
   float* db_partials;    // (splits, b, h, n, n) fp32, used when splits > 1
   int splits;

@@ -81,14 +81,41 @@ __device__ __forceinline__ void axpy_smem(float a, const float* sm, float* reg) 
 // rowfull[b, i] = 1 when every key of pair row i is masked.
 // ---------------------------------------------------------------------------
 __global__ void rowfull_kernel(MaskView mask, int n, int n_rows, uint8_t* rowfull,
-                               uint32_t* maskbits, uint32_t* maskbits_lin, int mask_words) {
+                               uint32_t* maskbits, uint32_t* maskbits_lin, int mask_words,
+                               uint32_t* rowrange) {
   const int bi = blockIdx.x;
   const int b = bi / n_rows, i = bi % n_rows;
   const uint8_t* row = mask.p + b * mask.sb + (int64_t)i * mask.si;
-  int open = 0;
-  for (int k = threadIdx.x; k < n; k += blockDim.x) open |= (row[k] == 0);
-  open = __syncthreads_or(open);
-  if (threadIdx.x == 0) rowfull[bi] = open ? 0 : 1;
+  __shared__ int first_open, last_open;
+  if (threadIdx.x == 0) {
+    first_open = n;
+    last_open = -1;
+  }
+  __syncthreads();
+  int lo = n, hi = -1;
+  for (int k = threadIdx.x; k < n; k += blockDim.x) {
+    if (row[k] == 0) {
+      lo = min(lo, k);
+      hi = max(hi, k);
+    }
+  }
+  if (hi >= 0) {
+    atomicMin(&first_open, lo);
+    atomicMax(&last_open, hi);
+  }
+  __syncthreads();
+  const int open = last_open >= 0;
+  if (threadIdx.x == 0) {
+    if (rowfull) rowfull[bi] = open ? 0 : 1;
+    // 128-key tiles [first, last + 1) that hold an open key: the tensor-core kernels walk
+    // only those.  A fully masked row weighs all n keys: every tile.
+    if (rowrange) {
+      const uint32_t t0 = open ? (uint32_t)(first_open >> 7) : 0u;
+      const uint32_t t1 = open ? (uint32_t)(last_open >> 7) + 1u : (uint32_t)((n + 127) >> 7);
+      rowrange[bi] = t0 | (t1 << 16);
+    }
+  }
+  if (!maskbits) return;
   // Packed key mask (bit set = key dropped or beyond n).  A fully masked row keeps
   // all n keys with uniform weight, so only the keys beyond n stay set.  Layout per
   // 128-key chunk c: word c*4 + jb holds, at bit l, key c*128 + 4*l + jb (the order
@@ -626,7 +653,7 @@ cudaError_t simt_forward(const FwdArgs& a, cudaStream_t s) {
 cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
   rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
-                                                      a.maskbits_lin, a.mask_words);
+                                                      a.maskbits_lin, a.mask_words, a.rowrange);
   if (a.bias_t) {
     dim3 grid((dm.n + 63) / 64, (dm.n + 63) / 64, dm.batch * dm.heads);
     bias_transpose_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_t, dm.heads, dm.n,
@@ -649,10 +676,14 @@ cudaError_t bwd_prepare(const BwdArgs& a, cudaStream_t s) {
 
 cudaError_t fwd_prepare(const FwdArgs& a, cudaStream_t s) {
   const Dims& dm = a.dm;
+  // the live key-tile range of every row always; the packed masks, row flags and the padded
+  // bias copy only where the workspace holds them (n % 8 != 0)
   rowfull_kernel<<<dm.batch * dm.n_rows, 128, 0, s>>>(a.mask, dm.n, dm.n_rows, a.rowfull, a.maskbits,
-                                                      nullptr, a.mask_words);
-  dim3 grid(1, dm.n, dm.batch * dm.heads);
-  bias_pad_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_pad, dm.heads, dm.n, dm.n_pad);
+                                                      nullptr, a.mask_words, a.rowrange);
+  if (a.bias_pad) {
+    dim3 grid(1, dm.n, dm.batch * dm.heads);
+    bias_pad_kernel<<<grid, 256, 0, s>>>(a.bias, (uint16_t*)a.bias_pad, dm.heads, dm.n, dm.n_pad);
+  }
   return cudaGetLastError();
 }
 

@@ -47,7 +47,8 @@ struct DbCfg {
   static constexpr int kThreads = 640;
   static constexpr uint64_t kSwz = RowSwizzle<D>::kDesc;
   static constexpr int kSbo = 8 * kRowBytes;
-  static int smem_bytes() { return 1024 + 1024 + NS * kStageBytes; }
+  static constexpr int kLiveBytes = 8192;   // one bit per row of the split (n_rows <= 65535)
+  static int smem_bytes() { return 1024 + 1024 + NS * kStageBytes + kLiveBytes; }
 };
 
 template <typename T, int D, int NS>
@@ -56,8 +57,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
              const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
              const __grid_constant__ CUtensorMap map_nlse, const __grid_constant__ CUtensorMap map_delta,
              View4 bias, const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits,
-             int mask_words, float* __restrict__ out, int splits, Dims dm,
-             unsigned int* status) {
+             int mask_words, const uint32_t* __restrict__ rowrange, float* __restrict__ out,
+             int splits, Dims dm, unsigned int* status) {
   using Cfg = DbCfg<D, NS>;
   constexpr int FULL = 0, EMPTY = FULL + NS, S_FULL = EMPTY + NS, S_FREE = S_FULL + 2,
                 NBARS = S_FREE + 2;
@@ -125,6 +126,24 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
+  // Rows of this split whose live key-tile range holds this item's key tile, one bit per
+  // row: the others weigh all 128 keys of the tile zero and add nothing to db, so no role
+  // touches them.  (A fully masked row's range is every tile.)
+  uint32_t* live = reinterpret_cast<uint32_t*>(gbase + tiles_off + NS * Cfg::kStageBytes);
+  {
+    const Item im = decode(blockIdx.x);
+    for (int w0 = warp * 32; w0 < im.nrows; w0 += 32 * (Cfg::kThreads / 32)) {
+      const int g = w0 + lane;
+      bool on = false;
+      if (g < im.nrows) {
+        const uint32_t v = rowrange ? __ldg(rowrange + im.b * dm.n_rows + im.i_begin + g) : 0xffff0000u;
+        on = (uint32_t)im.kt >= (v & 0xffffu) && (uint32_t)im.kt < (v >> 16);
+      }
+      const uint32_t bits = __ballot_sync(0xffffffffu, on);
+      if (lane == 0) live[w0 >> 5] = bits;
+    }
+  }
+  auto is_live = [&](int g) -> bool { return (live[g >> 5] >> (g & 31)) & 1u; };
   if (warp == kTmaWarp && lane == 0) {
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_do);
@@ -144,9 +163,10 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
         const Item im = decode(blockIdx.x);
-        for (int g = 0; g < im.nrows; ++g) {
+        for (int r = 0, g = 0; r < im.nrows; ++r) {
+          if (!is_live(r)) continue;
           {
-            const int s = g % NS, i = im.i_begin + g;
+            const int s = g % NS, i = im.i_begin + r;
             if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) break;
             mbar_arrive_expect_tx(bar(FULL + s), Cfg::kStageBytes);
             tma_load_5d(q_tile(s), &map_q, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
@@ -156,6 +176,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             tma_load_4d(base + nlse_off(s), &map_nlse, bar(FULL + s), im.jt * 128, i, im.h, im.b);
             tma_load_4d(base + delta_off(s), &map_delta, bar(FULL + s), im.jt * 128, i, im.h, im.b);
           }
+          ++g;
         }
       }
     } else if (warp == kMmaWarp) {
@@ -166,7 +187,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         bool ok = true;
         {
           const int nrows = decode(blockIdx.x).nrows;
-          for (int g = 0; g < nrows && ok; ++g) {
+          for (int r = 0, g = 0; r < nrows && ok; ++r) {
+            if (!is_live(r)) continue;
             const int s = g % NS, u = g & 1;
             ok = mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag);
             if (ok && g >= 2) ok = mbar_wait(bar(S_FREE + u), ((g >> 1) - 1) & 1, abort_flag);
@@ -186,6 +208,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             }
             umma_commit(bar(S_FULL + u));
             umma_commit(bar(EMPTY + s));
+            ++g;
           }
         }
       }
@@ -238,8 +261,9 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
         }
       }
-      for (int g = 0; g < im.nrows; ++g) {
-        const int s = g % NS, u = g & 1, i = im.i_begin + g;
+      for (int r = 0, g = 0; r < im.nrows; ++r) {
+        if (!is_live(r)) continue;
+        const int s = g % NS, u = g & 1, i = im.i_begin + r;
         // per-row inputs that do not come through shared memory (consumed after the
         // barrier waits below, which hide their latency)
         const uint32_t mw =
@@ -303,6 +327,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             }
           }
         }
+        ++g;
       }
       if (ok && n_store > 0) {
         if (n_store == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -377,7 +402,8 @@ cudaError_t launch_db(const BwdArgs& a, cudaStream_t stream) {
     bias.sb = bias.sh * dm.heads;
   }
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mdo, mk, mv, mnl, mdl, bias, a.rowfull,
-                                              a.maskbits_lin, a.mask_words, out, a.splits, dm, a.status);
+                                              a.maskbits_lin, a.mask_words, a.rowrange, out, a.splits,
+                                              dm, a.status);
   return cudaGetLastError();
 }
 

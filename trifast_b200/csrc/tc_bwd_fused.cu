@@ -102,8 +102,8 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                const __grid_constant__ CUtensorMap map_bt, const __grid_constant__ CUtensorMap map_lse,
                const __grid_constant__ CUtensorMap map_delta, View5 dq, View5 dk, View5 dv,
                const uint8_t* __restrict__ rowfull, const uint32_t* __restrict__ maskbits_lin,
-               int mask_words, Dims dm, FusedGrid grid, float* __restrict__ kv_scratch,
-               unsigned int* status) {
+               int mask_words, const uint32_t* __restrict__ rowrange, Dims dm, FusedGrid grid,
+               float* __restrict__ kv_scratch, unsigned int* status) {
   using Cfg = FusedCfg<D, NS, SB>;
   // Barriers.  The per-step ones exist once per step parity (index g & 1, phase
   // (g >> 1) & 1), which leaves every waiter a whole step of slack before a parity
@@ -148,6 +148,14 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     it.h = bh % dm.heads;
     it.b = bh / dm.heads;
     return it;
+  };
+  // Key tiles [lo, hi) of the item's row that hold an open key, as lo | hi << 16: the roles
+  // walk only those (dK, dV of the others are zero-filled, dQ gets nothing from them).
+  // Fetched one item ahead.
+  auto item_range = [&](int w) -> uint32_t {
+    if (rowrange == nullptr || w >= grid.total) return (uint32_t)nkt << 16;
+    const Item it = decode(w);
+    return __ldg(rowrange + it.b * dm.n_rows + it.i);
   };
 
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
@@ -199,11 +207,14 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       const bool leader = lane == 0;
       int g = 0, ktg = 0;  // running step and key-tile counters (barrier phases)
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
         const Item im = decode(w);
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         for (int c = 0; c < nch && ok; ++c) {
         const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
-        for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
           if (ktg >= 2)
             ok = __all_sync(0xffffffffu,
@@ -241,10 +252,13 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       constexpr uint32_t idesc_s = make_idesc(128, kBJ, kBf16, false, false);
       int g = 0, ktg = 0;
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         for (int c = 0; c < nch && ok; ++c) {
         const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
-        for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
           for (int js = js0; js < js1; ++js, ++g) {
             const int s = g % NS;
@@ -286,10 +300,13 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       constexpr uint32_t kStep16Rows = (16 * Cfg::kRowBytes) >> 4;
       int g = 0, ktg = 0;
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         for (int c = 0; c < nch && ok; ++c) {
         const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
-        for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++ktg) {
           for (int js = js0; js < js1; ++js, ++g) {
             const int s = g % NS;
             // the first accumulating MMAs of a key tile overwrite dK, dV: the epilogue
@@ -328,17 +345,20 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       constexpr uint32_t kStep16Rows = (16 * Cfg::kRowBytes) >> 4;
       int g = 0, ktg = 0, pgc = 0, chg = 0;  // chg: running chunk counter (DQ_FREE phases)
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         for (int c = 0; c < nch && ok; ++c, ++chg) {
         const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
-        for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++ktg) {
           const int kvb = ktg & 1;
           for (int js = js0; js < js1; ++js, ++g) {
             const bool with_dq = ((js - js0) & 1) || js == js1 - 1;
             const int pr = (js - js0) >> 1, pb = (pgc + pr) & 1;
             // the first dQ MMA of a chunk overwrites dQ: the previous chunk's epilogue must
             // have read it
-            const bool first = with_dq && kt == 0 && pr == 0 && chg > 0;
+            const bool first = with_dq && kt == kt_lo && pr == 0 && chg > 0;
             ok = mbar_wait_spin2(bar(P_READY + (g & 1)), (g >> 1) & 1, first, bar(DQ_FREE),
                                  (chg - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -356,7 +376,7 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
                 for (int ks = 0; ks < kBKeys / 16; ++ks)
                   umma_ss(tmem_base + Cfg::kDqCol + pr * Cfg::kAcc, a_ds + ks * ((16 * 128) >> 4),
-                          b_k + ks * kStep16Rows, idesc_dq, (kt > 0 || ks > 0) ? 1u : 0u);
+                          b_k + ks * kStep16Rows, idesc_dq, (kt > kt_lo || ks > 0) ? 1u : 0u);
               }
               umma_commit(bar(ACC_DONE + (g & 1)));
               if (js == js1 - 1) umma_commit(bar(KV_EMPTY + kvb));  // last read of this K, V
@@ -385,9 +405,23 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
       int g = 0, ktg = 0, pgc = 0;
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < grid.total && ok; w += gridDim.x) {
         const Item im = decode(w);
         const int i = im.i, b = im.b, h = im.h;
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
+        // dK (warps 0-3) and dV (warps 4-7) of the key tiles nobody walks: zero
+        for (int kt = 0; kt < nkt; ++kt) {
+          const int key = kt * kBKeys + t;
+          if ((kt < kt_lo || kt >= kt_hi) && key < n) {
+            const View5& out = half ? dv : dk;
+            T* dst = reinterpret_cast<T*>(out.p) + b * out.sb + h * out.sh + (int64_t)i * out.si +
+                     (int64_t)key * out.sj;
+#pragma unroll
+            for (int e = 0; e < D; e += 8) *reinterpret_cast<uint4*>(dst + e) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         const bool row_full = rowfull[b * dm.n_rows + i] != 0;
         // key mask of the row in key order (bit set = key dropped or beyond n; on a
         // fully masked row only the keys beyond n): word kt * 4 + wq covers this warp's
@@ -395,11 +429,11 @@ tc_dqkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         const uint32_t* mrow = maskbits_lin + ((int64_t)b * dm.n_rows + i) * mask_words;
         for (int c = 0; c < nch && ok; ++c) {
         const int js0 = c * jsc, js1 = min(njs, js0 + jsc);
-        uint32_t mword_next = __ldg(mrow + wq);
+        uint32_t mword_next = __ldg(mrow + kt_lo * 4 + wq);
 
-        for (int kt = 0; kt < nkt && ok; ++kt, ++ktg) {
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++ktg) {
           const uint32_t mword = mword_next;
-          if (kt + 1 < nkt) mword_next = __ldg(mrow + (kt + 1) * 4 + wq);
+          if (kt + 1 < kt_hi) mword_next = __ldg(mrow + (kt + 1) * 4 + wq);
           const int key = kt * kBKeys + t;
           const bool dropped = ((mword >> lane) & 1u) != 0u;
           // The key weight pattern is fixed for the whole query loop of a key tile, so
@@ -692,8 +726,8 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
   if (sms > kFusedMaxCtas) sms = kFusedMaxCtas;  // the dK / dV scratch is sized for this many CTAs
   const int ctas = grid.total < sms ? grid.total : sms;
   kern<<<ctas, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dq, a.dk, a.dv,
-                                              a.rowfull, a.maskbits_lin, a.mask_words, dm, grid,
-                                              a.kv_scratch, a.status);
+                                              a.rowfull, a.maskbits_lin, a.mask_words, a.rowrange, dm,
+                                              grid, a.kv_scratch, a.status);
   return cudaGetLastError();
 }
 

@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(R * 128 + 128, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_b,
               View5 o, float* __restrict__ lse, MaskView mask, const uint8_t* __restrict__ ws_rowfull,
-              const uint32_t* __restrict__ ws_maskbits, int ws_mask_words, Dims dm, ItemGrid items,
+              const uint32_t* __restrict__ ws_maskbits, int ws_mask_words,
+              const uint32_t* __restrict__ ws_rowrange, Dims dm, ItemGrid items,
               unsigned int* status) {
   using Cfg = FwdCfg<D, R, NS>;
   static_assert(R == 2, "two slots: the exp phases alternate between them");
@@ -151,6 +152,21 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     return it;
   };
   auto slot_row = [&](const Item& it, int r) -> int { return min(it.i0 + r, dm.n_rows - 1); };
+  // Key tiles [lo, hi) an item walks, as lo | hi << 16: the union of the live ranges of its
+  // rows (tiles outside it hold no open key of either row and weigh exactly zero).  Every
+  // role fetches the next item's range while it works on the current one.
+  auto item_range = [&](int w) -> uint32_t {
+    if (ws_rowrange == nullptr || w >= items.total) return (uint32_t)nkt << 16;
+    const Item it = decode(w);
+    uint32_t lo = 0xffffu, hi = 0u;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t v = __ldg(ws_rowrange + it.b * dm.n_rows + slot_row(it, r));
+      lo = min(lo, v & 0xffffu);
+      hi = max(hi, v >> 16);
+    }
+    return lo | (hi << 16);
+  };
 
   // A wait that gave up in an earlier CTA or launch leaves the status word set:
   // stop doing work until the host has read and cleared it.
@@ -198,14 +214,17 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (lane == 0) {
       int g = 0, it = 0;  // running key-tile and item counters (barrier phases)
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
         const Item im = decode(w);
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         if (it > 0) ok = mbar_wait(bar(Q_EMPTY), (it - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(bar(Q_FULL), R * Cfg::kTileBytes);
         for (int r = 0; r < R; ++r)
           tma_load_5d(q_tile(r), &map_q, bar(Q_FULL), 0, im.jt * kBJ, slot_row(im, r), im.h, im.b);
-        for (int kt = 0; kt < nkt; ++kt, ++g) {
+        for (int kt = kt_lo; kt < kt_hi; ++kt, ++g) {
           const int s = g % NS;
           if (g >= NS) ok = mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag);
           if (!ok) break;
@@ -238,7 +257,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       };
       int g = 0, it = 0;
       bool ok = true;
+      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
+        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        rng_next = item_range(w + gridDim.x);
         // S of the item's first key tile: needs Q, the first stage, and the S columns
         // released by the softmax of the previous item's last tile
         ok = mbar_wait(bar(Q_FULL), it & 1, abort_flag) &&
@@ -247,21 +269,21 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         issue_qk(g % NS);
-        if (nkt == 1) umma_commit(bar(Q_EMPTY));
-        for (int kt = 0; kt < nkt && ok; ++kt, ++g) {
+        if (kt_hi - kt_lo == 1) umma_commit(bar(Q_EMPTY));
+        for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++g) {
           const int s = g % NS;
-          if (kt + 1 < nkt) {
+          if (kt + 1 < kt_hi) {
             const int ns = (g + 1) % NS;
             ok = mbar_wait(bar(FULL + ns), ((g + 1) / NS) & 1, abort_flag) &&
                  mbar_wait(bar(S_FREE + r), g & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             issue_qk(ns);
-            if (kt + 2 == nkt) umma_commit(bar(Q_EMPTY));  // last read of this item's Q tile
+            if (kt + 2 == kt_hi) umma_commit(bar(Q_EMPTY));  // last read of this item's Q tile
           }
           ok = mbar_wait(bar(P_READY + r), g & 1, abort_flag);
           // the first PV of an item overwrites O: the previous item's epilogue must have read it
-          if (ok && kt == 0 && it > 0) ok = mbar_wait(bar(O_FREE + r), (it - 1) & 1, abort_flag);
+          if (ok && kt == kt_lo && it > 0) ok = mbar_wait(bar(O_FREE + r), (it - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -269,7 +291,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const uint64_t bd = make_smem_desc(v_tile(s, r) + ks * 16 * Cfg::kRowBytes, Cfg::kSbo,
                                                Cfg::kSbo, Cfg::kSwz);
             umma_ts(tmem_base + r * 256 + 192, tmem_base + r * 256 + 128 + ks * 8, bd, idesc_pv,
-                    (kt > 0 || ks > 0) ? 1u : 0u);
+                    (kt > kt_lo || ks > 0) ? 1u : 0u);
           }
           umma_commit(bar(O_DONE + r));
           umma_commit(bar(EMPTY + s));
@@ -345,8 +367,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     constexpr bool ahead = MB == 2;
     RowMask next_mask{mb, false};
     if (ahead && (int)blockIdx.x < items.total) next_mask = row_mask(blockIdx.x, mb);
+    uint32_t rng_next = item_range(blockIdx.x);
     for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
       const Item im = decode(w);
+      const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+      rng_next = item_range(w + gridDim.x);
       const int i = slot_row(im, r);
       const bool do_store = im.i0 + r < dm.n_rows;
       const int b = im.b, h = im.h, jt = im.jt;
@@ -360,7 +385,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       // loop, or the 128 live scores get duplicated and spill.
       auto key_loop = [&](auto row_full_tag) {
       constexpr bool kRowFull = decltype(row_full_tag)::value;
-      for (int kt = 0; kt < nkt; ++kt, ++g) {
+      for (int kt = kt_lo; kt < kt_hi; ++kt, ++g) {
         const int s = g % NS;
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
         if (!ok) break;
@@ -445,7 +470,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const float alpha = ex2((m_run - m_new) * kLog2e);
         m_run = m_new;
 
-        if (kt > 0) {
+        if (kt > kt_lo) {
           // PV of the previous key tile must be done before O is rescaled and P reused.
           ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + r), (g - 1) & 1, abort_flag));
           if (!ok) break;
@@ -614,7 +639,8 @@ cudaError_t launch(const FwdArgs& a, cudaStream_t stream) {
   items.total = items.njt * items.nrp * dm.batch * dm.heads;
   const int grid = items.total < sm_count() ? items.total : sm_count();
   kern<<<grid, Cfg::kThreads, smem, stream>>>(mq, mk, mv, mbias, a.o, a.lse, a.mask, a.rowfull,
-                                              a.maskbits, a.mask_words, dm, items, a.status);
+                                              a.maskbits, a.mask_words, a.rowrange, dm, items,
+                                              a.status);
   return cudaGetLastError();
 }
 

@@ -109,7 +109,7 @@ def _triangle_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: to
     o = torch.empty((bs, h, n_rows, n, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((bs, h, n_rows, n), dtype=torch.float32, device=q.device)
     shp = _lib.make_shape(bs, h, n, n_rows, d, q.dtype)
-    ws_bytes = lib.trifast_forward_workspace_bytes(C.byref(shp))   # 0 unless n % 8 != 0 on tensor cores
+    ws_bytes = lib.trifast_forward_workspace_bytes(C.byref(shp))   # 0 on the CUDA-core plan
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
     with torch.cuda.device(q.device):
         rc = lib.trifast_forward(C.byref(shp), C.byref(_lib.t5(q)), C.byref(_lib.t5(k)),
