@@ -143,7 +143,8 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       if (lane == 0) live[w0 >> 5] = bits;
     }
   }
-  auto is_live = [&](int g) -> bool { return (live[g >> 5] >> (g & 31)) & 1u; };
+  // (the roles walk the set bits word by word: one shared-memory read per 32 rows, nothing
+  // per row)
   if (warp == kTmaWarp && lane == 0) {
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_do);
@@ -163,11 +164,16 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
       // ---------------------------------------------------------- TMA producer
       if (lane == 0) {
         const Item im = decode(blockIdx.x);
-        for (int r = 0, g = 0; r < im.nrows; ++r) {
-          if (!is_live(r)) continue;
+        int g = 0;
+        bool stop = false;
+        for (int r0 = 0; r0 < im.nrows && !stop; r0 += 32) {
+        for (uint32_t bits = live[r0 >> 5]; bits != 0u; bits &= bits - 1u) {
           {
-            const int s = g % NS, i = im.i_begin + r;
-            if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) break;
+            const int s = g % NS, i = im.i_begin + r0 + __ffs(bits) - 1;
+            if (g >= NS && !mbar_wait(bar(EMPTY + s), ((g / NS) - 1) & 1, abort_flag)) {
+              stop = true;
+              break;
+            }
             mbar_arrive_expect_tx(bar(FULL + s), Cfg::kStageBytes);
             tma_load_5d(q_tile(s), &map_q, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
             tma_load_5d(do_tile(s), &map_do, bar(FULL + s), 0, im.jt * 128, i, im.h, im.b);
@@ -178,6 +184,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
           ++g;
         }
+        }
       }
     } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------- MMA issuer
@@ -187,8 +194,9 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
         bool ok = true;
         {
           const int nrows = decode(blockIdx.x).nrows;
-          for (int r = 0, g = 0; r < nrows && ok; ++r) {
-            if (!is_live(r)) continue;
+          int g = 0;
+          for (int r0 = 0; r0 < nrows && ok; r0 += 32) {
+          for (uint32_t bits = live[r0 >> 5]; bits != 0u && ok; bits &= bits - 1u) {
             const int s = g % NS, u = g & 1;
             ok = mbar_wait(bar(FULL + s), (g / NS) & 1, abort_flag);
             if (ok && g >= 2) ok = mbar_wait(bar(S_FREE + u), ((g >> 1) - 1) & 1, abort_flag);
@@ -209,6 +217,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
             umma_commit(bar(S_FULL + u));
             umma_commit(bar(EMPTY + s));
             ++g;
+          }
           }
         }
       }
@@ -261,9 +270,10 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
         }
       }
-      for (int r = 0, g = 0; r < im.nrows; ++r) {
-        if (!is_live(r)) continue;
-        const int s = g % NS, u = g & 1, i = im.i_begin + r;
+      int g = 0;
+      for (int r0 = 0; r0 < im.nrows && ok; r0 += 32) {
+      for (uint32_t bits = live[r0 >> 5]; bits != 0u; bits &= bits - 1u) {
+        const int s = g % NS, u = g & 1, i = im.i_begin + r0 + __ffs(bits) - 1;
         // per-row inputs that do not come through shared memory (consumed after the
         // barrier waits below, which hide their latency)
         const uint32_t mw =
@@ -328,6 +338,7 @@ tc_db_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ 
           }
         }
         ++g;
+      }
       }
       if (ok && n_store > 0) {
         if (n_store == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {

@@ -153,8 +153,14 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   };
   auto slot_row = [&](const Item& it, int r) -> int { return min(it.i0 + r, dm.n_rows - 1); };
   // Key tiles [lo, hi) an item walks, as lo | hi << 16: the union of the live ranges of its
-  // rows (tiles outside it hold no open key of either row and weigh exactly zero).  Every
-  // role fetches the next item's range while it works on the current one.
+  // rows (tiles outside it hold no open key of either row and weigh exactly zero).  Only the
+  // producer computes it (one item ahead; it alone is off the critical path) and hands it to
+  // the other roles through a shared-memory word per item parity, written before its arrive
+  // on Q_FULL: the issuers read it after their wait on Q_FULL, the softmax warps after the
+  // item's first S_FULL, which the issuers' MMAs complete.  The producer is never more than
+  // one item ahead of the issuers (Q_EMPTY) nor the issuers of the softmax warps (S_FREE),
+  // so a word is rewritten only after every reader of its previous value has moved on.
+  volatile uint32_t* rng_word = reinterpret_cast<volatile uint32_t*>(gbase + 264);   // [2]
   auto item_range = [&](int w) -> uint32_t {
     if (ws_rowrange == nullptr || w >= items.total) return (uint32_t)nkt << 16;
     const Item it = decode(w);
@@ -217,10 +223,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
         const Item im = decode(w);
-        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
+        const uint32_t rng = rng_next;
+        const int kt_lo = rng & 0xffffu, kt_hi = rng >> 16;
         rng_next = item_range(w + gridDim.x);
         if (it > 0) ok = mbar_wait(bar(Q_EMPTY), (it - 1) & 1, abort_flag);
         if (!ok) break;
+        rng_word[it & 1] = rng;
         mbar_arrive_expect_tx(bar(Q_FULL), R * Cfg::kTileBytes);
         for (int r = 0; r < R; ++r)
           tma_load_5d(q_tile(r), &map_q, bar(Q_FULL), 0, im.jt * kBJ, slot_row(im, r), im.h, im.b);
@@ -257,10 +265,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       };
       int g = 0, it = 0;
       bool ok = true;
-      uint32_t rng_next = item_range(blockIdx.x);
       for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
-        const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
-        rng_next = item_range(w + gridDim.x);
         // S of the item's first key tile: needs Q, the first stage, and the S columns
         // released by the softmax of the previous item's last tile
         ok = mbar_wait(bar(Q_FULL), it & 1, abort_flag) &&
@@ -268,6 +273,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
              (g == 0 || mbar_wait(bar(S_FREE + r), (g - 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
+        const uint32_t rng = rng_word[it & 1];
+        const int kt_lo = rng & 0xffffu, kt_hi = rng >> 16;
         issue_qk(g % NS);
         if (kt_hi - kt_lo == 1) umma_commit(bar(Q_EMPTY));
         for (int kt = kt_lo; kt < kt_hi && ok; ++kt, ++g) {
@@ -367,11 +374,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     constexpr bool ahead = MB == 2;
     RowMask next_mask{mb, false};
     if (ahead && (int)blockIdx.x < items.total) next_mask = row_mask(blockIdx.x, mb);
-    uint32_t rng_next = item_range(blockIdx.x);
     for (int w = blockIdx.x; w < items.total && ok; w += gridDim.x, ++it) {
       const Item im = decode(w);
-      const int kt_lo = rng_next & 0xffffu, kt_hi = rng_next >> 16;
-      rng_next = item_range(w + gridDim.x);
       const int i = slot_row(im, r);
       const bool do_store = im.i0 + r < dm.n_rows;
       const int b = im.b, h = im.h, jt = im.jt;
@@ -385,11 +389,18 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       // loop, or the 128 live scores get duplicated and spill.
       auto key_loop = [&](auto row_full_tag) {
       constexpr bool kRowFull = decltype(row_full_tag)::value;
-      for (int kt = kt_lo; kt < kt_hi; ++kt, ++g) {
+      // (the item's tile range is read after its first S_FULL: see rng_word)
+      int kt_lo = -1, kt_hi = 1;
+      for (int kt = 0; kt < kt_hi; ++kt, ++g) {
         const int s = g % NS;
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + r), g & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
+        if (kt_lo < 0) {
+          const uint32_t rng = rng_word[it & 1];
+          kt_lo = kt = rng & 0xffffu;
+          kt_hi = rng >> 16;
+        }
         float x[128];
         {
           uint32_t* xr = reinterpret_cast<uint32_t*>(x);
