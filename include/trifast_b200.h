@@ -139,9 +139,10 @@ int trifast_pick_plan(const trifast_shape* shape, trifast_plan* plan);
  * db and its row-split partials, bias copies).  Returns 0 on an invalid shape. */
 size_t trifast_backward_workspace_bytes(const trifast_shape* shape);
 
-/* Bytes of workspace the forward needs: 0 except on the tensor-core path with
- * n % 8 != 0, which reads the bias through a copy with a 16-byte row pitch and the
- * key mask through packed words (both made inside trifast_forward). */
+/* Bytes of workspace the forward needs: 0 on the CUDA-core plan.  On the tensor-core
+ * plan: one word per pair row (the range of 128-key tiles that hold an open key; tiles
+ * outside it are not walked), and for n % 8 != 0 also a copy of the bias with a 16-byte
+ * row pitch and the key mask as packed words (all made inside trifast_forward). */
 size_t trifast_forward_workspace_bytes(const trifast_shape* shape);
 
 /* Forward: o = softmax_k(q.k^T * d^-0.5 + bias + mask) v and lse (natural log).
