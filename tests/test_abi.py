@@ -328,3 +328,11 @@ def test_extent_one_dimensions_get_canonical_strides():
     assert _prep5(q).data_ptr() == q.data_ptr()                 # 16-byte multiples: passed as is
     m = torch.zeros(2, 1, 1, dtype=torch.bool).as_strided((2, 1, 1), (1, 7, 7))
     assert _prep_mask(m).stride() == (1, 1, 1)
+
+
+def test_copy_blocks_argument_checks():
+    lib = _lib.load()
+    f = lib.trifast_copy_blocks
+    assert f(None, 64, 0x1000, 64, 64, 2, 0, None) == -1            # NULL
+    assert f(0x1000, 32, 0x2000, 64, 64, 2, 0, None) == -5          # blocks would overlap
+    assert f(0x1000, 64, 0x2000, 64, 0, 2, 0, None) == 0            # nothing to copy

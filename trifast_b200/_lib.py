@@ -56,6 +56,8 @@ SIGNATURES = {
     "trifast_version": (C.c_int, []),
     "trifast_status_str": (C.c_char_p, [C.c_int]),
     "trifast_last_cuda_error": (C.c_char_p, []),
+    "trifast_copy_blocks": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t,
+                                      C.c_size_t, C.c_int, C.c_void_p]),
     "trifast_pick_plan": (C.c_int, [_P(Shape), _P(Plan)]),
     "trifast_backward_workspace_bytes": (C.c_size_t, [_P(Shape)]),
     "trifast_forward_workspace_bytes": (C.c_size_t, [_P(Shape)]),

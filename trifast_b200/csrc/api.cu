@@ -315,6 +315,16 @@ extern "C" {
 
 int trifast_version(void) { return 100; }
 
+int trifast_copy_blocks(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                        size_t block_bytes, size_t blocks, int to_host, void* stream) {
+  if (!dst || !src) return TRIFAST_ERR_NULL;
+  if (block_bytes == 0 || blocks == 0) return TRIFAST_OK;
+  if (dst_pitch < block_bytes || src_pitch < block_bytes) return TRIFAST_ERR_STRIDE;
+  return cuda_rc(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, block_bytes, blocks,
+                                   to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
+                                   (cudaStream_t)stream));
+}
+
 const char* trifast_last_cuda_error(void) { return cudaGetErrorName(g_last_cuda_error); }
 
 const char* trifast_status_str(int status) {

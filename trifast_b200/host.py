@@ -91,14 +91,26 @@ class HostPipeline:
     def _vlse(self, slot, r):
         return self._lse[slot][: self.batch * self.heads * r * self.n]
 
-    def _copy_rows(self, dst5, src5, r0, r1, to_host):
-        """One asynchronous copy per (batch, head): each is a dense block on both sides."""
-        for b in range(self.batch):
-            for h in range(self.heads):
-                if to_host:
-                    dst5[b, h, r0:r1].copy_(src5[b, h], non_blocking=True)
-                else:
-                    dst5[b, h].copy_(src5[b, h, r0:r1], non_blocking=True)
+    def _copy_rows(self, dst5, src5, r0, r1, to_host, stream):
+        """Rows r0:r1 of every (batch, head) between a host tensor and a slot buffer: one 2-D
+        transfer per batch entry (a block per head; all of them in one when the batch entries
+        are evenly spaced too), enqueued on ``stream``."""
+        host, devt = (dst5, src5) if to_host else (src5, dst5)
+        es = host.element_size()
+        block = (r1 - r0) * self.n * self.d * es
+        even = self.batch == 1 or host.stride(0) == self.heads * host.stride(1)
+        groups = [(0, self.batch * self.heads)] if even else \
+            [(b, self.heads) for b in range(self.batch)]
+        for first, count in groups:
+            b0 = first if not even else 0
+            hp = host[b0, 0, r0].data_ptr()
+            dp = devt[b0, 0].data_ptr()
+            rc = self.lib.trifast_copy_blocks(
+                C.c_void_p(hp if to_host else dp), C.c_size_t(host.stride(1) * es if to_host else block),
+                C.c_void_p(dp if to_host else hp), C.c_size_t(block if to_host else host.stride(1) * es),
+                C.c_size_t(block), C.c_size_t(count), C.c_int(1 if to_host else 0),
+                C.c_void_p(stream.cuda_stream))
+            _lib.check(rc, "trifast_copy_blocks")
 
     def run(self, q, k, v, bias, mask, do=None, out=None, group=None):
         """q, k, v (and do): pinned (batch, heads, rows, n, d); bias: pinned
@@ -158,7 +170,7 @@ class HostPipeline:
                     if c >= self.slots:
                         self.s_in.wait_event(ev_run[c - self.slots])   # inputs of the slot consumed
                     for nm in (_NAMES_IN if bwd else ("q", "k", "v")):
-                        self._copy_rows(self._v5(nm, slot, r), src[nm], r0, r1, to_host=False)
+                        self._copy_rows(self._v5(nm, slot, r), src[nm], r0, r1, False, self.s_in)
                     for b in range(B):
                         self._vmask(slot, r)[b].copy_(m8[b, r0:r1], non_blocking=True)
                     ev_in[c] = self.s_in.record_event()
@@ -203,7 +215,7 @@ class HostPipeline:
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(ev_run[c])
                     for nm in (_NAMES_OUT if bwd else ("o",)):
-                        self._copy_rows(out[nm], self._v5(nm, slot, r), r0, r1, to_host=True)
+                        self._copy_rows(out[nm], self._v5(nm, slot, r), r0, r1, True, self.s_out)
                     ev_out[c] = self.s_out.record_event()
             if bwd:
                 with torch.cuda.stream(self.s_run):
