@@ -722,9 +722,19 @@ cudaError_t launch_fused(const BwdArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
-  sms = sms - a.reserve_sms > 0 ? sms - a.reserve_sms : 1;
   if (sms > kFusedMaxCtas) sms = kFusedMaxCtas;  // the dK / dV scratch is sized for this many CTAs
-  const int ctas = grid.total < sms ? grid.total : sms;
+  int ctas = grid.total < sms ? grid.total : sms;
+  if (a.reserve_sms > 0) {
+    // A collective runs beside this kernel: leave it SMs.  Every CTA walks its items one
+    // after the other, so the kernel lasts ceil(items / CTAs) items: keep at least
+    // `reserve_sms` SMs free, then drop every further CTA that does not shorten that.
+    // (Measured on 4 GPUs, n = 1024: with 8 SMs free the kernel takes 8 rounds instead of 7,
+    // +0.11 ms, and the all-reduce stays hidden; with 1 SM free it keeps 7 rounds but the
+    // all-reduce crawls and 0.20 ms of it show after the kernel.)
+    const int keep = sms - a.reserve_sms > 0 ? sms - a.reserve_sms : 1;
+    const int waves = (grid.total + keep - 1) / keep;
+    ctas = (grid.total + waves - 1) / waves;
+  }
   kern<<<ctas, Cfg::kThreads, smem, stream>>>(mk, mv, mq, mdo, mbt, mlse, mdelta, a.dq, a.dk, a.dv,
                                               a.rowfull, a.maskbits_lin, a.mask_words, a.rowrange, dm,
                                               grid, a.kv_scratch, a.status);
