@@ -47,11 +47,12 @@ def test_version_and_status_strings():
     (32, 4, 32, torch.float32, _lib.KERNEL_SIMT),     # fp32 always on CUDA cores
     (1024, 4, 32, torch.float32, _lib.KERNEL_SIMT),
     (191, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),  # ragged n: padded bias copy in the workspace
-    (100, 4, 32, torch.bfloat16, _lib.KERNEL_SIMT),
-    (64, 1, 64, torch.bfloat16, _lib.KERNEL_SIMT),    # below one tile
+    (100, 4, 32, torch.bfloat16, _lib.KERNEL_TCGEN05),  # one tile, partly filled
+    (64, 1, 64, torch.bfloat16, _lib.KERNEL_TCGEN05),   # smallest n on tensor cores
+    (63, 1, 64, torch.bfloat16, _lib.KERNEL_SIMT),      # a tile less than a quarter full
     (256, 4, 128, torch.bfloat16, _lib.KERNEL_SIMT),
     (256, 4, 16, torch.float16, _lib.KERNEL_TCGEN05),  # 32-byte rows
-    (64, 4, 16, torch.float16, _lib.KERNEL_SIMT),
+    (48, 4, 16, torch.float16, _lib.KERNEL_SIMT),
 ])
 def test_heuristic_table(n, h, d, dtype, kernel):
     plan = _lib.pick_plan(1, h, n, n, d, dtype)
@@ -70,12 +71,12 @@ def test_forward_workspace_sizes():
         C.byref(_lib.make_shape(1, 4, n, n, 32, dtype)))
     assert size(1024) == 4096 and size(1000) == 4096          # 4 bytes x 1000 rows -> 4096
     assert size(1001) > 4 * 1001 * 1008 * 2 and size(191) > 4 * 191 * 192 * 2   # + bias copy
-    assert size(100) == 0                                     # below one tile: CUDA cores
+    assert size(48) == 0                                      # below a quarter tile: CUDA cores
     assert size(1001, torch.float32) == 0
 
 
 def test_heuristic_rejects_impossible_forced_kernel():
-    shp = _lib.make_shape(1, 4, 100, 100, 32, torch.bfloat16, _lib.KERNEL_TCGEN05)
+    shp = _lib.make_shape(1, 4, 48, 48, 32, torch.bfloat16, _lib.KERNEL_TCGEN05)
     plan = _lib.Plan()
     assert _lib.load().trifast_pick_plan(C.byref(shp), C.byref(plan)) == -10
 

@@ -320,7 +320,7 @@ def _random_square_cases(count=32, seed=77):
                          _random_square_cases(int(os.environ.get("TRIFAST_B200_FUZZ_DRAWS", "32"))))
 def test_random_square_problems_through_the_public_op(idx, n, h, d, bs, dtype, mask, layout, std):
     """Seeded random whole problems through `triangle_attention` + autograd (every kernel family:
-    n < 128 and d = 16 / 128 on CUDA cores, the rest on tensor cores), batch 1-2, dense or
+    n < 64, d = 128 and fp32 on CUDA cores, the rest on tensor cores), batch 1-2, dense or
     permuted-projection layouts, masks that drop the head or the tail of the keys, input scale
     0.5-2 (flat to peaked softmax), against the fp64 oracle."""
     g = torch.Generator().manual_seed(5000 + idx)

@@ -201,7 +201,7 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   // tile gain nothing from it.  (n % 8 != 0 runs on it through a padded bias copy in
   // the workspace: TMA needs a 16-byte row pitch.)  The two-kernel backward has no
   // d = 16 tiles.
-  const bool tc_ok = half && (s->d == 16 || s->d == 32 || s->d == 64) && s->n >= 128 &&
+  const bool tc_ok = half && (s->d == 16 || s->d == 32 || s->d == 64) && s->n >= kMinTensorCoreN &&
                      !(s->d == 16 && (s->flags & TRIFAST_FLAG_SPLIT_BWD));
   int kernel = s->kernel;
   if (kernel == TRIFAST_KERNEL_AUTO) kernel = tc_ok ? TRIFAST_KERNEL_TCGEN05 : TRIFAST_KERNEL_SIMT;

@@ -10,6 +10,10 @@
 
 namespace trifast {
 
+// Smallest n the tensor-core kernels take: one 128 x 128 tile at least a quarter full.
+constexpr int kMinTensorCoreN = 64;
+
+
 // (b, h, i, j, d) view with element strides; d contiguous.
 struct View5 {
   char* p;

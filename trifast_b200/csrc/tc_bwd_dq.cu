@@ -513,7 +513,7 @@ bool tc_backward_supported(const BwdArgs& a) {
   const Dims& dm = a.dm;
   if (a.dtype != TRIFAST_BF16 && a.dtype != TRIFAST_F16) return false;
   if (dm.d != 16 && dm.d != 32 && dm.d != 64) return false;  // (d = 16: one-pass kernel only)
-  if (dm.n < 128) return false;
+  if (dm.n < kMinTensorCoreN) return false;
   if (!a.maskbits || !a.rowfull || !a.delta || !a.neg_lse2) return false;
   // the bias goes through TMA: 16-byte row pitch, or the padded copy from the workspace
   const bool bias_tma_ok = !(((uintptr_t)a.bias.p) & 15) && (a.bias.sj * 2) % 16 == 0 &&

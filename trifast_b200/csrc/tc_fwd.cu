@@ -716,7 +716,7 @@ bool make_tensor_map_f32(CUtensorMap* map, int rank, void* base, const uint64_t*
 bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a) {
   if (dtype != TRIFAST_BF16 && dtype != TRIFAST_F16) return false;
   if (dm.d != 16 && dm.d != 32 && dm.d != 64) return false;
-  if (dm.n < 128) return false;
+  if (dm.n < kMinTensorCoreN) return false;
   const int smem = (dm.d == 16)   ? FwdCfg<16, 2, 3>::smem_bytes(dm.n)
                    : (dm.d == 32) ? FwdCfg<32, 2, 3>::smem_bytes(dm.n)
                                   : FwdCfg<64, 2, 2>::smem_bytes(dm.n);
