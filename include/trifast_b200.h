@@ -109,7 +109,7 @@ typedef struct trifast_mask {
 
 /* Tile plan chosen by the heuristic (host only; no device needed). */
 typedef struct trifast_plan {
-  int32_t kernel;        /* trifast_kernel actually used */
+  int32_t kernel;        /* trifast_kernel actually used (by the backward, when the two differ) */
   int32_t block_j;       /* query tile */
   int32_t block_k;       /* key tile */
   int32_t rows_per_cta;  /* pair rows sharing one bias tile in the forward */
@@ -117,6 +117,8 @@ typedef struct trifast_plan {
   int32_t db_row_splits; /* row groups whose db partials are summed in fixed order */
   int32_t bwd_fused;     /* 1: dq, dk, dv come from one kernel (one exponential per score) */
   int32_t bwd_chunks;    /* query chunks a row is walked in by that kernel (1: dQ of a row fits TMEM) */
+  int32_t fwd_kernel;    /* trifast_kernel of the forward: differs from `kernel` for head dim 128,
+                            whose forward has tensor-core tiles and whose backward has not */
 } trifast_plan;
 
 /* Library version as major*10000 + minor*100 + patch. */

@@ -47,7 +47,7 @@ class PushReduce(C.Structure):
 class Plan(C.Structure):
     _fields_ = [("kernel", C.c_int32), ("block_j", C.c_int32), ("block_k", C.c_int32),
                 ("rows_per_cta", C.c_int32), ("stages", C.c_int32), ("db_row_splits", C.c_int32),
-                ("bwd_fused", C.c_int32), ("bwd_chunks", C.c_int32)]
+                ("bwd_fused", C.c_int32), ("bwd_chunks", C.c_int32), ("fwd_kernel", C.c_int32)]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/trifast_b200.h

@@ -129,26 +129,27 @@ struct Workspace {
 struct FwdWorkspace {
   size_t rowrange_off, rowfull_off, maskbits_off, bias_pad_off, total;
   int mask_words;
-  bool ragged;
+  bool masks, bias_pad;   // the packed masks and row flags / the padded bias copy are present
 };
 
 FwdWorkspace carve_fwd(const trifast_shape* s, const trifast_plan& plan) {
   FwdWorkspace w{};
   w.mask_words = ((s->n + 127) / 128) * 4;
-  if (plan.kernel != TRIFAST_KERNEL_TCGEN05) return w;
+  if (plan.fwd_kernel != TRIFAST_KERNEL_TCGEN05) return w;
   size_t off = 0;
   w.rowrange_off = off;
   off = (off + (size_t)s->batch * s->n_rows * sizeof(uint32_t) + 255) / 256 * 256;
   w.total = off;
-  w.ragged = s->n % 8 != 0;
-  if (!w.ragged) return w;
+  w.bias_pad = s->n % 8 != 0;
+  w.masks = w.bias_pad || s->d == 128;   // the head-dim-128 forward always reads prepared masks
+  if (!w.masks) return w;
   const size_t n_pad = (size_t)(s->n + 7) / 8 * 8;
   w.rowfull_off = off;
   off = (off + (size_t)s->batch * s->n_rows + 255) / 256 * 256;
   w.maskbits_off = off;
   off = (off + (size_t)s->batch * s->n_rows * w.mask_words * sizeof(uint32_t) + 255) / 256 * 256;
   w.bias_pad_off = off;
-  off = (off + (size_t)s->batch * s->heads * s->n * n_pad * 2 + 255) / 256 * 256;
+  if (w.bias_pad) off = (off + (size_t)s->batch * s->heads * s->n * n_pad * 2 + 255) / 256 * 256;
   w.total = off;
   return w;
 }
@@ -203,10 +204,15 @@ int pick_plan(const trifast_shape* s, trifast_plan* p) {
   // d = 16 tiles.
   const bool tc_ok = half && (s->d == 16 || s->d == 32 || s->d == 64) && s->n >= kMinTensorCoreN &&
                      !(s->d == 16 && (s->flags & TRIFAST_FLAG_SPLIT_BWD));
+  // Head dim 128 has tensor-core tiles in the forward only: its backward stays on the CUDA
+  // cores (`kernel`), and asking for the tensor-core family fails in the backward entry points.
+  const bool tc_fwd_only = half && s->d == 128 && s->n >= kMinTensorCoreN;
   int kernel = s->kernel;
   if (kernel == TRIFAST_KERNEL_AUTO) kernel = tc_ok ? TRIFAST_KERNEL_TCGEN05 : TRIFAST_KERNEL_SIMT;
-  if (kernel == TRIFAST_KERNEL_TCGEN05 && !tc_ok) return TRIFAST_ERR_KERNEL_CHOICE;
+  if (kernel == TRIFAST_KERNEL_TCGEN05 && !tc_ok && !tc_fwd_only) return TRIFAST_ERR_KERNEL_CHOICE;
+  if (tc_fwd_only) kernel = TRIFAST_KERNEL_SIMT;
   p->kernel = kernel;
+  p->fwd_kernel = (tc_fwd_only && s->kernel != TRIFAST_KERNEL_SIMT) ? TRIFAST_KERNEL_TCGEN05 : kernel;
   if (kernel == TRIFAST_KERNEL_TCGEN05) {
     p->block_j = 128;
     p->block_k = 128;
@@ -264,6 +270,9 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
     return rc;
   if (o && (rc = check_t5(o, shape))) return rc;
   if (!lse) return TRIFAST_ERR_NULL;
+  // (head dim 128: tensor-core tiles exist for the forward only)
+  if (shape->kernel == TRIFAST_KERNEL_TCGEN05 && c.plan.kernel != TRIFAST_KERNEL_TCGEN05)
+    return TRIFAST_ERR_KERNEL_CHOICE;
   const Workspace w = carve(shape, c.plan);
   if (!workspace || workspace_bytes < w.total) return TRIFAST_ERR_WORKSPACE;
   if (((uintptr_t)workspace) & 255) return TRIFAST_ERR_ALIGN;
@@ -393,20 +402,22 @@ int trifast_forward(const trifast_shape* shape, const trifast_t5* q, const trifa
   if (w.total) {
     char* base = (char*)workspace;
     a.rowrange = (uint32_t*)(base + w.rowrange_off);
-    if (w.ragged) {
+    if (w.masks) {
       a.rowfull = (uint8_t*)(base + w.rowfull_off);
       a.maskbits = (uint32_t*)(base + w.maskbits_off);
-      a.bias_pad = (void*)(base + w.bias_pad_off);
     }
+    if (w.bias_pad) a.bias_pad = (void*)(base + w.bias_pad_off);
   }
   cudaStream_t s = (cudaStream_t)stream;
-  if (c.plan.kernel == TRIFAST_KERNEL_TCGEN05) {
-    if (!tc_forward_supported(c.dm, shape->dtype, &a)) {
+  if (c.plan.fwd_kernel == TRIFAST_KERNEL_TCGEN05) {
+    const bool d128 = c.dm.d == 128;
+    if (!(d128 ? tc_forward_d128_supported(c.dm, shape->dtype, &a)
+               : tc_forward_supported(c.dm, shape->dtype, &a))) {
       if (shape->kernel == TRIFAST_KERNEL_TCGEN05) return TRIFAST_ERR_KERNEL_CHOICE;
       return cuda_rc(simt_forward(a, s));
     }
     if (w.total && (rc = cuda_rc(fwd_prepare(a, s)))) return rc;
-    return cuda_rc(tc_forward(a, c.plan, s));
+    return cuda_rc(d128 ? tc_forward_d128(a, s) : tc_forward(a, c.plan, s));
   }
   return cuda_rc(simt_forward(a, s));
 }

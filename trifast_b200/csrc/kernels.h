@@ -62,6 +62,8 @@ cudaError_t db_cast(const float* db_f32, View4 db, int dtype, int batch, int hea
                     cudaStream_t s);
 
 // tcgen05 kernels (tc_*.cu): bf16 / fp16.
+bool tc_forward_d128_supported(const Dims& dm, int dtype, const FwdArgs* a);
+cudaError_t tc_forward_d128(const FwdArgs& a, cudaStream_t s);
 bool tc_forward_supported(const Dims& dm, int dtype, const FwdArgs* a);
 cudaError_t tc_forward(const FwdArgs& a, const trifast_plan& plan, cudaStream_t s);
 bool tc_backward_supported(const BwdArgs& a);
