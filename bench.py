@@ -256,7 +256,7 @@ class DirectStep:
         # launches per step: forward 1 (+ the live key-tile ranges of the rows on the tensor-core
         # path, + the padded bias copy for n % 8 != 0); backward: row flags + packed mask, bias
         # transpose (tensor-core path only), delta, db, split reduce (if split), dq, dk/dv, cast
-        self.launches = 1 + ((1 + (1 if n % 8 else 0)) if plan["kernel"] == 2 else 0)
+        self.launches = 1 + ((1 + (1 if n % 8 else 0)) if plan["fwd_kernel"] == 2 else 0)
         if w.backward:
             self.launches += 1 + (1 if plan["kernel"] == 2 else 0) + 1 + 1 + \
                 (1 if plan["db_row_splits"] > 1 else 0) + (1 if plan["bwd_fused"] else 2) + 1
@@ -526,7 +526,7 @@ def run_native(args, w):
         # kernels the phase holds both and S, dP are executed twice: still 10 algorithmic);
         # db recomputes S and dP = 4 executed, none of them algorithmic beyond the 10.
         kernels_flops = {"forward": flops_fwd(w)}
-        names = {"forward": "tc_fwd_kernel"}
+        names = {"forward": "tc_fwd_d128_kernel" if w.d == 128 else "tc_fwd_kernel"}
         if w.backward:
             kernels_flops["backward_dqkv"] = 2.5 * flops_fwd(w)
             names["backward_dqkv"] = "tc_dqkv_kernel" if step.plan["bwd_fused"] else \

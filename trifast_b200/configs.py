@@ -41,6 +41,10 @@ WORKLOADS = {
                                     "random:0.05", bias_std=2.0, backward=False),
     # Large-complex training step, last 10 % padded.
     "c5_n2048_pad": Workload("c5_n2048_pad", 2048, 4, 32, torch.bfloat16, "padding:0.90"),
+    # Head dim 128, inference-only forward: the one head dim of the reference's test matrix at
+    # which the contraction, not the exponentials, is the larger load.
+    "d128_n1024_fwd": Workload("d128_n1024_fwd", 1024, 4, 128, torch.bfloat16, "none",
+                               backward=False),
     # Headline metric shape.
     "metric_n1024": Workload("metric_n1024", 1024, 4, 32, torch.bfloat16, "none"),
 }
