@@ -43,6 +43,14 @@ static_assert(256 * kRegInc + 128 * kRegDec <= 384 * 168, "setmaxnreg pool");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMaxInit = -1e30f;
+// A key tile moves a row's running maximum only when it exceeds it by more than kLazyTau
+// (natural-log units): weights then reach e^kLazyTau instead of 1, which 16-bit P holds with
+// the same relative precision, and the 128-column rescale of O (a TMEM round trip of the
+// whole accumulator) runs for the first tiles of a row only instead of nearly every tile.
+#ifndef TRIFAST_D128_LAZY_TAU
+#define TRIFAST_D128_LAZY_TAU 5.5f
+#endif
+constexpr float kLazyTau = TRIFAST_D128_LAZY_TAU;
 constexpr int kTileBytes = 128 * kD * 2;     // Q, K or V tile: two halves of 16 KiB
 constexpr int kHalfBytes = 16384;
 constexpr int kBiasBytes = 128 * 128 * 2;    // two [128 queries x 64 keys] boxes
@@ -362,7 +370,7 @@ tc_fwd_d128_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           mx[0] = fmax3(mx[0], x[124], x[125]);
           mx[1] = fmax3(mx[1], x[126], x[127]);
           const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          const float m_new = (mt > m_run) ? mt : m_run;
+          const float m_new = (mt > m_run + kLazyTau) ? mt : m_run;
           const float neg = -m_new * kLog2e;
           // (difference first: exactly 1 when the maximum stays, also at its initial value)
           const float alpha = ex2((m_run - m_new) * kLog2e);
