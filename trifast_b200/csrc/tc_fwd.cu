@@ -57,12 +57,14 @@ constexpr int kBJ = 128, kBK = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMaxInit = -1e30f;
-// A tile moves the running maximum only when it exceeds it by more than kLazyTau
+// A tile moves the running maximum only when it exceeds it by more than the lazy threshold
 // (natural-log units).  0 = always track the exact maximum: the largest weight of a
 // row is then exactly 1 before rounding to 16 bits, which keeps the error of peaked
 // rows lowest; a positive value (FlashAttention-style lazy rescale) trades that for
-// fewer rescales of O.
-constexpr float kLazyTau = 0.f;
+// fewer rescales of O.  Measured at n = 1024: 2.7 % of the forward at d = 64 (64 columns of
+// O per rescale), 1.5 % at d = 32, 1 % at d = 16, for a maximum error against the fp64 oracle
+// about a third larger: taken at d = 64 only.
+template <int D> constexpr float lazy_tau() { return D >= 64 ? 5.5f : 0.f; }
 constexpr int kSmemLimit = 232448;  // 227 KiB opt-in limit per CTA
 constexpr int kHeaderBytes = 512;
 
@@ -472,8 +474,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         mx[0] = fmax3(mx[0], x[124], x[125]);
         mx[1] = fmax3(mx[1], x[126], x[127]);
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        // running maximum (see kLazyTau)
-        const float m_new = (mt > m_run + kLazyTau) ? mt : m_run;
+        // running maximum (see lazy_tau)
+        const float m_new = (mt > m_run + lazy_tau<D>()) ? mt : m_run;
         const float neg = -m_new * kLog2e;
         // (difference first: exactly 1 when the maximum stays, also at the initial value,
         // where a fused m_run * log2e + neg would leave the rounding residue of 1e30 * log2e
