@@ -235,7 +235,9 @@ class DirectStep:
         self.o = torch.empty_like(q)
         self.lse = torch.empty((bs, h, rows, n), dtype=torch.float32, device=dev)
         self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype,
-                                     flags=_lib.FLAG_SHARE_GPU if group_size > 1 else None)
+                                     flags=_lib.share_gpu_flags(
+                                         8 if db_reduce == "push" else share_policy(group_size)[1])
+                                     if group_size > 1 else None)   # (the push kernel's 8 CTAs run at once)
         self.fws_bytes = self.lib.trifast_forward_workspace_bytes(C.byref(self.shape))
         self.fws = torch.empty(self.fws_bytes, dtype=torch.uint8, device=dev) if self.fws_bytes else None
         if w.backward:
@@ -348,6 +350,15 @@ def quantiles(xs):
     return {"p10": pick(0.1), "p50": pick(0.5), "p90": pick(0.9)}
 
 
+def share_policy(world):
+    """(NCCL CTA cap, SMs the dq/dk/dv kernel leaves free) for the db all-reduce.  The NCCL
+    kernel only runs beside the dq/dk/dv kernel when it finds as many free SMs as it has
+    CTAs (measured on 4 GPUs: 2 CTAs on 1 free SM did not start before that kernel ended, 0.67
+    of 0.67 ms exposed; 4 CTAs on 1 SM: 0.29 of 0.34 ms), so both numbers are the same; with 8
+    the all-reduce (0.2 ms alone) ends well inside the kernel at every N."""
+    return 8, 8
+
+
 def run_native(args, w):
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))
@@ -358,8 +369,9 @@ def run_native(args, w):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # the db all-reduce runs beside the dq/dk/dv kernels, which leave 8 SMs free for it
-        os.environ.setdefault("NCCL_MAX_CTAS", "8")
+        # the db all-reduce runs beside the dq/dk/dv kernels, which leave SMs free for it: as
+        # many as NCCL may use CTAs (see share_policy)
+        os.environ.setdefault("NCCL_MAX_CTAS", str(share_policy(world)[0]))
         dist.init_process_group("nccl", device_id=dev)
     from trifast_b200.dist import shard_rows, triangle_attention_row_sharded
     rows = shard_rows(w.n, rank, world)
@@ -570,7 +582,10 @@ def run_native(args, w):
             "vs_baseline": None, "dtype": str(w.dtype).replace("torch.", ""),
             "data": "synthetic",
             "config": dict(workload_config(w, world),
-                           **({"db_reduce": args.db_reduce} if world > 1 and w.backward else {})),
+                           **({"db_reduce": args.db_reduce,
+                               "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
+                               "free_sms": 8 if args.db_reduce == "push" else share_policy(world)[1]}
+                              if world > 1 and w.backward else {})),
             "plan": step.plan, "clocks": clocks,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -76,6 +76,9 @@ typedef enum trifast_flags {
    * at once instead of after it.  (No reference counterpart: the reference is single-GPU.) */
   TRIFAST_FLAG_SHARE_GPU = 2
 } trifast_flags;
+/* With TRIFAST_FLAG_SHARE_GPU, bits 8-15 of `flags` hold the number of SMs to leave free
+ * (0 = 8): as many as the collective beside the kernel has CTAs that must run at once. */
+#define TRIFAST_FLAG_SHARE_SMS(sms) (((sms) & 0xff) << 8)
 
 /* Problem extents, shared by every call. */
 typedef struct trifast_shape {

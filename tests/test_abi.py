@@ -337,3 +337,17 @@ def test_copy_blocks_argument_checks():
     assert f(None, 64, 0x1000, 64, 64, 2, 0, None) == -1            # NULL
     assert f(0x1000, 32, 0x2000, 64, 64, 2, 0, None) == -5          # blocks would overlap
     assert f(0x1000, 64, 0x2000, 64, 0, 2, 0, None) == 0            # nothing to copy
+
+
+def test_share_gpu_flag_carries_the_number_of_free_sms():
+    lib = _lib.load()
+    plan = _lib.Plan()
+    ok = lambda flags: lib.trifast_pick_plan(
+        C.byref(_lib.make_shape(1, 4, 256, 256, 32, torch.bfloat16, flags=flags)), C.byref(plan))
+    assert _lib.share_gpu_flags() == _lib.FLAG_SHARE_GPU
+    assert _lib.share_gpu_flags(1) == _lib.FLAG_SHARE_GPU | 0x100
+    assert ok(_lib.share_gpu_flags(1)) == 0 and ok(_lib.share_gpu_flags(20)) == 0
+    assert ok(0x100) == -10                       # a count without the flag
+    assert ok(0x10000) == -10                     # unknown bit
+    with pytest.raises(ValueError):
+        _lib.share_gpu_flags(256)

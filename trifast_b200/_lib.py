@@ -17,6 +17,13 @@ LIB_PATH = os.path.join(_HERE, "libtrifast_b200.so")
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
 FLAG_SPLIT_BWD, FLAG_SHARE_GPU = 1, 2   # trifast_flags of the header
+
+
+def share_gpu_flags(free_sms: int = 0) -> int:
+    """TRIFAST_FLAG_SHARE_GPU with the number of SMs to leave free (0: the library's 8)."""
+    if not 0 <= free_sms <= 255:
+        raise ValueError("free_sms must be 0..255")
+    return FLAG_SHARE_GPU | (free_sms << 8)
 STATIC_SCRATCH_BYTES = 16 << 20   # TRIFAST_STATIC_SCRATCH_BYTES of the header
 _KERNEL_ENV = {"": 0, "auto": 0, "simt": 1, "tcgen05": 2}
 

@@ -60,7 +60,8 @@ int check_shape(const trifast_shape* s) {
   if (s->dtype < TRIFAST_F32 || s->dtype > TRIFAST_F16) return TRIFAST_ERR_DTYPE;
   if (s->kernel < TRIFAST_KERNEL_AUTO || s->kernel > TRIFAST_KERNEL_TCGEN05)
     return TRIFAST_ERR_KERNEL_CHOICE;
-  if (s->flags & ~(TRIFAST_FLAG_SPLIT_BWD | TRIFAST_FLAG_SHARE_GPU)) return TRIFAST_ERR_KERNEL_CHOICE;
+  if (s->flags & ~(TRIFAST_FLAG_SPLIT_BWD | TRIFAST_FLAG_SHARE_GPU | 0xff00)) return TRIFAST_ERR_KERNEL_CHOICE;
+  if ((s->flags & 0xff00) && !(s->flags & TRIFAST_FLAG_SHARE_GPU)) return TRIFAST_ERR_KERNEL_CHOICE;
   return TRIFAST_OK;
 }
 
@@ -301,7 +302,9 @@ int fill_bwd(const trifast_shape* shape, const Common& c, const trifast_t5* d_o,
   a->splits = c.plan.db_row_splits;
   a->dm = c.dm;
   a->dtype = shape->dtype;
-  a->reserve_sms = (shape->flags & TRIFAST_FLAG_SHARE_GPU) ? kSharedGpuSms : 0;
+  a->reserve_sms = (shape->flags & TRIFAST_FLAG_SHARE_GPU)
+                       ? (((shape->flags >> 8) & 0xff) ? ((shape->flags >> 8) & 0xff) : kSharedGpuSms)
+                       : 0;
   a->status = c.status;
   return TRIFAST_OK;
 }

@@ -41,10 +41,11 @@ class CudaKernels:
     def forward(self, q, k, v, b, mask):
         return _triangle_attention(q, k, v, b, mask)
 
-    def __init__(self, share_gpu: bool = False):
+    def __init__(self, share_gpu: bool = False, free_sms: int = 0):
         # under a process group the all-reduce of db runs beside the dq/dk/dv kernels:
-        # they then leave a few SMs free for it (TRIFAST_FLAG_SHARE_GPU)
-        self.flags = _lib.flags_choice() | (_lib.FLAG_SHARE_GPU if share_gpu else 0)
+        # they then leave a few SMs free for it (TRIFAST_FLAG_SHARE_GPU; free_sms = 0: the
+        # library's 8, which suits a collective of up to 8 CTAs)
+        self.flags = _lib.flags_choice() | (_lib.share_gpu_flags(free_sms) if share_gpu else 0)
 
     def _common(self, do, q, k, v, b, mask):
         bs, h, n_rows, n, d = _check_inputs(q, k, v, b, mask)
