@@ -224,7 +224,7 @@ def workload_config(w, gpus):
 class DirectStep:
     """fwd (+bwd) through the C ABI with every buffer preallocated."""
 
-    def __init__(self, w, q, k, v, b, m, do, group_size, db_reduce="nccl"):
+    def __init__(self, w, q, k, v, b, m, do, group_size, db_reduce="nccl", push_ctas=4, free_sms=8):
         from trifast_b200 import _lib
         self.lib, self._lib = _lib.load(), _lib
         self.w, self.world = w, group_size
@@ -235,9 +235,7 @@ class DirectStep:
         self.o = torch.empty_like(q)
         self.lse = torch.empty((bs, h, rows, n), dtype=torch.float32, device=dev)
         self.shape = _lib.make_shape(bs, h, n, rows, d, q.dtype,
-                                     flags=_lib.share_gpu_flags(
-                                         8 if db_reduce == "push" else share_policy(group_size)[1])
-                                     if group_size > 1 else None)   # (the push kernel's 8 CTAs run at once)
+                                     flags=_lib.share_gpu_flags(free_sms) if group_size > 1 else None)
         self.fws_bytes = self.lib.trifast_forward_workspace_bytes(C.byref(self.shape))
         self.fws = torch.empty(self.fws_bytes, dtype=torch.uint8, device=dev) if self.fws_bytes else None
         if w.backward:
@@ -266,7 +264,7 @@ class DirectStep:
         self.reducer = None
         if w.backward and group_size > 1 and db_reduce == "push":
             from trifast_b200.dist import PushReducer
-            self.reducer = PushReducer(self.db32.numel(), dev)
+            self.reducer = PushReducer(self.db32.numel(), dev, ctas=push_ctas)
 
     def forward(self):
         a, B = self.a, C.byref
@@ -380,7 +378,10 @@ def run_native(args, w):
     q, k, v, b, m, do = make_inputs(w, seed=0, rows=rows if (world > 1 or args.rows) else None,
                                     device=dev)
     torch.cuda.synchronize()
-    step = DirectStep(w, q, k, v, b, m, do, world, args.db_reduce)
+    free_sms = args.free_sms or share_policy(world)[1]
+    if args.db_reduce == "push" and args.push_ctas > free_sms:
+        raise SystemExit("--push-ctas must not exceed --free-sms: the exchange kernel's CTAs run at once")
+    step = DirectStep(w, q, k, v, b, m, do, world, args.db_reduce, args.push_ctas, free_sms)
 
     def barrier():
         torch.cuda.synchronize()
@@ -584,7 +585,7 @@ def run_native(args, w):
             "config": dict(workload_config(w, world),
                            **({"db_reduce": args.db_reduce,
                                "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
-                               "free_sms": 8 if args.db_reduce == "push" else share_policy(world)[1]}
+                               "free_sms": free_sms, "push_ctas": args.push_ctas}
                               if world > 1 and w.backward else {})),
             "plan": step.plan, "clocks": clocks,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -627,6 +628,10 @@ def main():
     ap.add_argument("--db-reduce", default="nccl", choices=["nccl", "push"],
                     help="N > 1: how the db partials of the row shards are summed: NCCL all-reduce "
                          "or the library's own peer-store exchange")
+    ap.add_argument("--push-ctas", type=int, default=4,
+                    help="CTAs (1024 threads each) of the peer-store exchange kernel (--db-reduce push)")
+    ap.add_argument("--free-sms", type=int, default=0,
+                    help="SMs the dq/dk/dv kernel leaves free for the db exchange at N > 1 (0: 8)")
     ap.add_argument("--rows", type=int, default=0,
                     help="profiling aid: only this many pair rows of the workload (a row shard on "
                          "one GPU; the printed line is then not the benchmark)")

@@ -224,7 +224,9 @@ int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
  * single-GPU (SURVEY of the reference: no distributed code). */
 typedef struct trifast_push_reduce {
   int32_t rank, world;      /* world <= 8 */
-  int32_t ctas;             /* CTAs to launch; 0 = 8 (it runs beside the dq/dk/dv kernel) */
+  int32_t ctas;             /* CTAs of 1024 threads to launch; 0 = 4.  They meet through a counter,
+                               so all of them must find a free SM at once: pass no more than the
+                               dq/dk/dv kernel beside them leaves free (TRIFAST_FLAG_SHARE_SMS) */
   uint32_t epoch;           /* same on every rank, +1 per call, never 0 */
   int64_t count;            /* fp32 elements of db */
   const float* partial;     /* this rank's partial sum (any local memory, 16-byte aligned) */

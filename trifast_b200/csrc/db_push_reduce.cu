@@ -6,7 +6,7 @@
 // memory; nothing loads from a peer, and no multicast is used.
 //
 // One launch per rank and step, all ranks at about the same time (right after their db
-// kernels), a few CTAs each, so that it runs beside the dq / dk / dv kernel on the SMs
+// kernels), one to a few CTAs of 1024 threads each, so that it runs beside the dq / dk / dv kernel on the SMs
 // that kernel leaves free.  Ranks meet twice through flag words in each other's memory
 // (epoch-valued, so they never need resetting): "my pushes into your staging area have
 // landed" and "my reduced slice has landed in your result".  Every wait is bounded: a
@@ -82,7 +82,7 @@ __device__ bool await(const PushReduceParams& p, int base, int* gave_up) {
   return *gave_up == 0;
 }
 
-__global__ void __launch_bounds__(512) db_push_reduce_kernel(PushReduceParams p, unsigned int* status) {
+__global__ void __launch_bounds__(1024) db_push_reduce_kernel(PushReduceParams p, unsigned int* status) {
   __shared__ int gave_up;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -162,8 +162,10 @@ cudaError_t db_push_reduce(const trifast_push_reduce* a, unsigned int* status, c
   p.rank = a->rank;
   p.world = a->world;
   p.epoch = a->epoch;
-  const int ctas = a->ctas > 0 ? a->ctas : 8;
-  db_push_reduce_kernel<<<ctas, 512, 0, s>>>(p, status);
+  // CTAs of 1024 threads: each needs an SM of its own, and all of them must run at once
+  // (they meet through a counter), so the caller passes no more than it keeps SMs free
+  const int ctas = a->ctas > 0 ? a->ctas : 4;
+  db_push_reduce_kernel<<<ctas, 1024, 0, s>>>(p, status);
   return cudaGetLastError();
 }
 

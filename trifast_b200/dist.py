@@ -116,8 +116,9 @@ class PushReducer:
 
     _FLAG_FLOATS = 64          # 16 flag words per rank, padded
 
-    def __init__(self, count: int, device: torch.device, group=None):
+    def __init__(self, count: int, device: torch.device, group=None, ctas: int = 4):
         import torch.distributed._symmetric_memory as symm
+        self.ctas = ctas      # CTAs of the exchange kernel: each wants a free SM, all at once
         self.lib = _lib.load()
         self.group = dist.group.WORLD if group is None else group
         self.world = dist.get_world_size(self.group)
@@ -146,7 +147,7 @@ class PushReducer:
         assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() == self.count
         self.epoch += 1
         a = _lib.PushReduce()
-        a.rank, a.world, a.ctas, a.epoch, a.count = self.rank, self.world, 8, self.epoch, self.count
+        a.rank, a.world, a.ctas, a.epoch, a.count = self.rank, self.world, self.ctas, self.epoch, self.count
         a.partial, a.counters = partial.data_ptr(), self.counters.data_ptr()
         for r in range(self.world):
             a.staging[r], a.result[r], a.flags[r] = self._staging[r], self._result[r], self._flags[r]
