@@ -221,7 +221,7 @@ int trifast_db_finalize(const trifast_shape* shape, const float* db_f32,
  * at zero and are never reset by the caller.  The ranks wait for each other inside the kernel
  * with a bounded wait (about 2 s): a rank that misses its peers sets the device status word
  * (trifast_check_device_status) and returns.  No reference counterpart: the reference is
- * single-GPU (SURVEY of the reference: no distributed code). */
+ * single-GPU and holds no distributed code. */
 typedef struct trifast_push_reduce {
   int32_t rank, world;      /* world <= 8 */
   int32_t ctas;             /* CTAs of 1024 threads to launch; 0 = 4.  They meet through a counter,
