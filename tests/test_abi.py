@@ -351,3 +351,22 @@ def test_share_gpu_flag_carries_the_number_of_free_sms():
     assert ok(0x10000) == -10                     # unknown bit
     with pytest.raises(ValueError):
         _lib.share_gpu_flags(256)
+
+
+def test_head_dim_128_plan_and_forward_workspace():
+    """d = 128: tensor-core tiles exist for the forward only.  plan.kernel (the backward's
+    family) is CUDA cores, plan.fwd_kernel tensor cores; the forward workspace always holds
+    the prepared row flags and packed masks (4 words per 128 keys and row) besides the ranges,
+    and the padded bias copy only for ragged n; asking for CUDA cores gives them throughout."""
+    lib = _lib.load()
+    plan = _lib.pick_plan(1, 4, 1024, 1024, 128, torch.bfloat16)
+    assert (plan["kernel"], plan["fwd_kernel"], plan["bwd_fused"]) == (_lib.KERNEL_SIMT, _lib.KERNEL_TCGEN05, 0)
+    assert _lib.pick_plan(1, 4, 1024, 1024, 128, torch.bfloat16, _lib.KERNEL_SIMT)["fwd_kernel"] == _lib.KERNEL_SIMT
+    assert _lib.pick_plan(1, 4, 1024, 1024, 128, torch.float32)["fwd_kernel"] == _lib.KERNEL_SIMT
+    assert _lib.pick_plan(1, 4, 48, 48, 128, torch.bfloat16)["fwd_kernel"] == _lib.KERNEL_SIMT
+    size = lambda n: lib.trifast_forward_workspace_bytes(C.byref(_lib.make_shape(1, 4, n, n, 128, torch.bfloat16)))
+    assert size(1024) == 4096 + 1024 + 1024 * 32 * 4                  # ranges, row flags, packed masks
+    assert size(1000) < 4 * 1000 * 1000 * 2 < size(1001)              # the bias copy only when ragged
+    # the backward of d = 128 has no tensor-core family to force
+    shp = _lib.make_shape(1, 4, 256, 256, 128, torch.bfloat16, _lib.KERNEL_TCGEN05)
+    assert lib.trifast_backward_workspace_bytes(C.byref(shp)) > 0     # sized for the CUDA-core kernels
