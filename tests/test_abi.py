@@ -370,3 +370,12 @@ def test_head_dim_128_plan_and_forward_workspace():
     # the backward of d = 128 has no tensor-core family to force
     shp = _lib.make_shape(1, 4, 256, 256, 128, torch.bfloat16, _lib.KERNEL_TCGEN05)
     assert lib.trifast_backward_workspace_bytes(C.byref(shp)) > 0     # sized for the CUDA-core kernels
+
+
+def test_host_pipeline_block_bounds():
+    from trifast_b200.host import block_bounds
+    for rows, chunk in ((1024, 64), (128, 32), (100, 64), (1000, 64), (50, 8), (7, 64), (200, 64), (129, 64)):
+        b = block_bounds(rows, chunk)
+        sizes = [b[i + 1] - b[i] for i in range(len(b) - 1)]
+        assert b[0] == 0 and b[-1] == rows and all(0 < x <= chunk for x in sizes), (rows, chunk, b)
+    assert [y - x for x, y in zip(block_bounds(1024, 64), block_bounds(1024, 64)[1:])][:3] == [16, 32, 64]

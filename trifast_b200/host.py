@@ -37,6 +37,28 @@ def _check_host5(name, t, shape, dtype):
         raise ValueError(f"{name}: the (rows, n, d) block of every (batch, head) must be contiguous")
 
 
+def block_bounds(rows: int, chunk: int) -> list:
+    """Row boundaries of the blocks a step is streamed in: blocks of ``chunk`` rows, but the
+    first and the last two are a quarter and a half of that.  The first block's copy in and
+    the last block's copy out have nothing to overlap with, so they are kept short; the blocks
+    in between keep the transfers long enough for the full PCIe rate."""
+    if rows <= 2 * chunk or chunk < 8:
+        edges = list(range(0, rows, chunk)) + [rows]
+        return edges
+    q, h = chunk // 4, chunk // 2
+    head = [0, q, q + h]
+    tail_start = rows - (q + h)
+    edges = head[:]
+    r = head[-1]
+    while r + chunk <= tail_start:
+        r += chunk
+        edges.append(r)
+    if r < tail_start:                       # what does not fill a whole block
+        edges.append(tail_start)
+    edges += [rows - q, rows]
+    return edges
+
+
 class HostPipeline:
     """Preallocated device buffers and streams for one problem shape.
 
@@ -47,7 +69,7 @@ class HostPipeline:
 
     def __init__(self, batch: int, heads: int, n: int, d: int, dtype: torch.dtype,
                  device: torch.device, rows: Optional[int] = None, chunk_rows: int = 64,
-                 slots: int = 3, backward: bool = True):
+                 slots: int = 3, backward: bool = True, ramp: bool = True):
         if slots < 2:
             raise ValueError("at least two slots are needed to overlap copies with compute")
         self.lib = _lib.load()
@@ -55,6 +77,7 @@ class HostPipeline:
         self.rows = n if rows is None else rows
         self.chunk = max(1, min(chunk_rows, self.rows))
         self.slots, self.backward = slots, backward
+        self.ramp = ramp          # short first and last blocks (see block_bounds)
         self.device = torch.device(device)
         es = torch.empty((), dtype=dtype).element_size()
         blk = batch * heads * self.chunk * n * d
@@ -151,7 +174,8 @@ class HostPipeline:
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_stream(cur)
         run_stream = C.c_void_p(self.s_run.cuda_stream)
-        nchunks = (R + self.chunk - 1) // self.chunk
+        bounds = block_bounds(R, self.chunk) if self.ramp else list(range(0, R, self.chunk)) + [R]
+        nchunks = len(bounds) - 1
         ev_in = [None] * nchunks
         ev_run = [None] * nchunks
         ev_out = [None] * nchunks
@@ -163,7 +187,7 @@ class HostPipeline:
             ab = L.t4(self.bias)
             for c in range(nchunks):
                 slot = c % self.slots
-                r0, r1 = c * self.chunk, min(R, (c + 1) * self.chunk)
+                r0, r1 = bounds[c], bounds[c + 1]
                 r = r1 - r0
                 # ---- host -> device
                 with torch.cuda.stream(self.s_in):
