@@ -455,6 +455,198 @@ __global__ void __launch_bounds__(BKT) simt_dkv_kernel(View5 q, View5 k, View5 v
 }
 
 // ---------------------------------------------------------------------------
+// dq and dk / dv for head dim 128: a row of 128 floats per operand and accumulator does not
+// fit the registers of one thread (the kernels above spill 8-10 KB per thread there), so G = 4
+// neighbouring lanes share a query (a key): lane p of the group owns the 16-byte chunks
+// p, p + 4, p + 8, ... of every row (neighbouring lanes read neighbouring chunks of a
+// shared-memory row: no bank conflicts), the partial dot products are summed over the group
+// with two shuffles, and every lane then holds the score.
+// ---------------------------------------------------------------------------
+template <int D, int G>
+struct GroupCols {
+  static constexpr int kChunks = D / (4 * G);   // 16-byte chunks per lane
+  static constexpr int kFloats = 4 * kChunks;
+};
+
+template <typename T, int D, int G>
+__device__ __forceinline__ void load_part(const T* row, int part, bool valid, float* reg) {
+#pragma unroll
+  for (int ci = 0; ci < GroupCols<D, G>::kChunks; ++ci) {
+    const int c0 = (ci * G + part) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) reg[4 * ci + e] = valid ? to_f32<T>(row[c0 + e]) : 0.f;
+  }
+}
+
+template <int D, int G>
+__device__ __forceinline__ float dot_part(const float* reg, const float* sm, int part) {
+  float acc = 0.f;
+  const float4* s4 = reinterpret_cast<const float4*>(sm);
+#pragma unroll
+  for (int ci = 0; ci < GroupCols<D, G>::kChunks; ++ci) {
+    const float4 x = s4[ci * G + part];
+    acc = fmaf(reg[4 * ci + 0], x.x, acc);
+    acc = fmaf(reg[4 * ci + 1], x.y, acc);
+    acc = fmaf(reg[4 * ci + 2], x.z, acc);
+    acc = fmaf(reg[4 * ci + 3], x.w, acc);
+  }
+  return acc;
+}
+
+template <int D, int G>
+__device__ __forceinline__ void axpy_part(float a, const float* sm, int part, float* reg) {
+  const float4* s4 = reinterpret_cast<const float4*>(sm);
+#pragma unroll
+  for (int ci = 0; ci < GroupCols<D, G>::kChunks; ++ci) {
+    const float4 x = s4[ci * G + part];
+    reg[4 * ci + 0] = fmaf(a, x.x, reg[4 * ci + 0]);
+    reg[4 * ci + 1] = fmaf(a, x.y, reg[4 * ci + 1]);
+    reg[4 * ci + 2] = fmaf(a, x.z, reg[4 * ci + 2]);
+    reg[4 * ci + 3] = fmaf(a, x.w, reg[4 * ci + 3]);
+  }
+}
+
+template <int G>
+__device__ __forceinline__ float group_sum(float x, unsigned gmask) {
+#pragma unroll
+  for (int o = 1; o < G; o <<= 1) x += __shfl_xor_sync(gmask, x, o);
+  return x;
+}
+
+template <typename T, int D, int G, int BJ, int BK>
+__global__ void __launch_bounds__(BJ * G) simt_dq_group_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                               MaskView mask, View5 d_o, View5 dq,
+                                                               const float* lse, const float* delta,
+                                                               const uint8_t* rowfull, Dims dm) {
+  constexpr int NT = BJ * G, W = GroupCols<D, G>::kFloats;
+  __shared__ __align__(16) float Ks[BK][D];
+  __shared__ __align__(16) float Vs[BK][D];
+  __shared__ uint8_t Ms[BK];
+  const int n = dm.n;
+  const int i = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x, part = tid % G;
+  const unsigned gmask = ((1u << G) - 1u) << ((tid & 31) & ~(G - 1));
+  const int j = blockIdx.x * BJ + tid / G;
+  const bool jvalid = j < n;
+  const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+  const float uniform = 1.f / (float)n;
+  const uint8_t* mrow = mask.p + b * mask.sb + (int64_t)i * mask.si;
+
+  float qr[W], gr[W], acc[W];
+  load_part<T, D, G>(row5<T>(q, b, h, i, jvalid ? j : 0), part, jvalid, qr);
+  load_part<T, D, G>(row5<T>(d_o, b, h, i, jvalid ? j : 0), part, jvalid, gr);
+#pragma unroll
+  for (int c = 0; c < W; ++c) acc[c] = 0.f;
+  const int64_t stat = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n + (jvalid ? j : 0);
+  const float my_lse = lse[stat];
+  const float my_delta =
+      delta[(((int64_t)b * dm.heads + h) * dm.n_rows + i) * dm.n_pad + (jvalid ? j : 0)];
+  const T* brow = row4<T>(bias, b, h, jvalid ? j : 0);
+
+  for (int k0 = 0; k0 < n; k0 += BK) {
+    __syncthreads();
+    const int valid = min(BK, n - k0);
+    stage_tile<T, D, BK, NT>(Ks, valid, [&](int r) { return row5<T>(k, b, h, i, k0 + r); });
+    stage_tile<T, D, BK, NT>(Vs, valid, [&](int r) { return row5<T>(v, b, h, i, k0 + r); });
+    for (int t = tid; t < BK; t += NT) Ms[t] = (t < valid) ? (row_full ? 0 : mrow[k0 + t]) : 1;
+    __syncthreads();
+#pragma unroll 2
+    for (int kk = 0; kk < BK; ++kk) {
+      const float s = group_sum<G>(dot_part<D, G>(qr, Ks[kk], part), gmask);
+      const float dp = group_sum<G>(dot_part<D, G>(gr, Vs[kk], part), gmask);
+      float p;
+      if (Ms[kk]) {
+        p = 0.f;
+      } else if (row_full) {
+        p = uniform;
+      } else {
+        const float bv = jvalid ? to_f32<T>(brow[k0 + kk]) : 0.f;
+        p = expf(fmaf(s, dm.scale, bv) - my_lse);
+      }
+      axpy_part<D, G>(p * (dp - my_delta), Ks[kk], part, acc);
+    }
+  }
+  if (jvalid) {
+    T* pdq = row5w<T>(dq, b, h, i, j);
+#pragma unroll
+    for (int ci = 0; ci < GroupCols<D, G>::kChunks; ++ci)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) pdq[(ci * G + part) * 4 + e] = from_f32<T>(acc[4 * ci + e] * dm.scale);
+  }
+}
+
+template <typename T, int D, int G, int BKT, int BJT>
+__global__ void __launch_bounds__(BKT * G) simt_dkv_group_kernel(View5 q, View5 k, View5 v, View4 bias,
+                                                                 MaskView mask, View5 d_o, View5 dk,
+                                                                 View5 dv, const float* lse,
+                                                                 const float* delta,
+                                                                 const uint8_t* rowfull, Dims dm) {
+  constexpr int NT = BKT * G, W = GroupCols<D, G>::kFloats;
+  __shared__ __align__(16) float Qs[BJT][D];
+  __shared__ __align__(16) float Gs[BJT][D];
+  __shared__ float Ls[BJT], Ds[BJT];
+  const int n = dm.n;
+  const int i = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / dm.heads, h = bh % dm.heads;
+  const int tid = threadIdx.x, part = tid % G;
+  const unsigned gmask = ((1u << G) - 1u) << ((tid & 31) & ~(G - 1));
+  const int key = blockIdx.x * BKT + tid / G;
+  const bool kvalid = key < n;
+  const bool row_full = rowfull[b * dm.n_rows + i] != 0;
+  const float uniform = 1.f / (float)n;
+  const bool masked =
+      !kvalid || (!row_full && mask.p[b * mask.sb + (int64_t)i * mask.si + key] != 0);
+
+  float kr[W], vr[W], acck[W], accv[W];
+  load_part<T, D, G>(row5<T>(k, b, h, i, kvalid ? key : 0), part, kvalid, kr);
+  load_part<T, D, G>(row5<T>(v, b, h, i, kvalid ? key : 0), part, kvalid, vr);
+#pragma unroll
+  for (int c = 0; c < W; ++c) {
+    acck[c] = 0.f;
+    accv[c] = 0.f;
+  }
+  const int64_t stat0 = (((int64_t)b * dm.heads + h) * dm.n_rows + i) * n;
+
+  for (int j0 = 0; j0 < n; j0 += BJT) {
+    __syncthreads();
+    const int valid = min(BJT, n - j0);
+    stage_tile<T, D, BJT, NT>(Qs, valid, [&](int r) { return row5<T>(q, b, h, i, j0 + r); });
+    stage_tile<T, D, BJT, NT>(Gs, valid, [&](int r) { return row5<T>(d_o, b, h, i, j0 + r); });
+    for (int t = tid; t < BJT; t += NT) {
+      Ls[t] = (t < valid) ? lse[stat0 + j0 + t] : 0.f;
+      Ds[t] = (t < valid) ? delta[stat0 / n * dm.n_pad + j0 + t] : 0.f;
+    }
+    __syncthreads();
+    if (masked) continue;  // exactly zero weight (the whole group: its lanes share the key)
+    for (int jj = 0; jj < valid; ++jj) {
+      const float s = group_sum<G>(dot_part<D, G>(kr, Qs[jj], part), gmask);
+      const float dp = group_sum<G>(dot_part<D, G>(vr, Gs[jj], part), gmask);
+      float p;
+      if (row_full) {
+        p = uniform;
+      } else {
+        const float bv = to_f32<T>(row4<T>(bias, b, h, j0 + jj)[key]);
+        p = expf(fmaf(s, dm.scale, bv) - Ls[jj]);
+      }
+      axpy_part<D, G>(p, Gs[jj], part, accv);
+      axpy_part<D, G>(p * (dp - Ds[jj]), Qs[jj], part, acck);
+    }
+  }
+  if (kvalid) {
+    T* pdk = row5w<T>(dk, b, h, i, key);
+    T* pdv = row5w<T>(dv, b, h, i, key);
+#pragma unroll
+    for (int ci = 0; ci < GroupCols<D, G>::kChunks; ++ci)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pdk[(ci * G + part) * 4 + e] = from_f32<T>(acck[4 * ci + e] * dm.scale);
+        pdv[(ci * G + part) * 4 + e] = from_f32<T>(accv[4 * ci + e]);
+      }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // db partials: CTA = (32 x 32 (j, k) tile, row split); 256 threads, 2 x 2 each.
 // ---------------------------------------------------------------------------
 template <typename T, int D>
@@ -722,8 +914,13 @@ cudaError_t simt_bwd_dq(const BwdArgs& a, cudaStream_t s) {
     constexpr int D = decltype(dc)::value;
     constexpr int BJ = 64, BK = (D <= 32) ? 32 : 16;
     dim3 gq((dm.n + BJ - 1) / BJ, dm.n_rows, dm.batch * dm.heads);
-    simt_dq_kernel<T, D, BJ, BK><<<gq, BJ, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.dq,
-                                                   a.lse, a.delta, a.rowfull, dm);
+    if constexpr (D == 128) {  // four lanes per query: a thread's rows stay in registers
+      simt_dq_group_kernel<T, D, 4, BJ, BK><<<gq, BJ * 4, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o,
+                                                                  a.dq, a.lse, a.delta, a.rowfull, dm);
+    } else {
+      simt_dq_kernel<T, D, BJ, BK><<<gq, BJ, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.dq,
+                                                     a.lse, a.delta, a.rowfull, dm);
+    }
   });
 }
 
@@ -734,8 +931,13 @@ cudaError_t simt_bwd_dkv(const BwdArgs& a, cudaStream_t s) {
     constexpr int D = decltype(dc)::value;
     constexpr int BKT = 64, BJT = (D <= 32) ? 32 : 16;
     dim3 gk((dm.n + BKT - 1) / BKT, dm.n_rows, dm.batch * dm.heads);
-    simt_dkv_kernel<T, D, BKT, BJT><<<gk, BKT, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o,
-                                                       a.dk, a.dv, a.lse, a.delta, a.rowfull, dm);
+    if constexpr (D == 128) {
+      simt_dkv_group_kernel<T, D, 4, BKT, BJT><<<gk, BKT * 4, 0, s>>>(
+          a.q, a.k, a.v, a.bias, a.mask, a.d_o, a.dk, a.dv, a.lse, a.delta, a.rowfull, dm);
+    } else {
+      simt_dkv_kernel<T, D, BKT, BJT><<<gk, BKT, 0, s>>>(a.q, a.k, a.v, a.bias, a.mask, a.d_o,
+                                                         a.dk, a.dv, a.lse, a.delta, a.rowfull, dm);
+    }
   });
 }
 
